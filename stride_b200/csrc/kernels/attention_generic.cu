@@ -15,6 +15,8 @@
 // Two optional rules on top: a cap c on the scores, s <- c tanh(s / c) after the scale; and a sink per query head, a
 // learned number whose exponential joins the softmax's denominator (it has no key and no value and is not scaled): it
 // enters the running maximum and sum after the last group of keys, so the order of the sums stays a function of p.
+// Values may be narrower or wider than keys (`vd` beside `hd`), and a head may take a penalty off a score in proportion
+// to the key's distance: s <- s - slope_h (p - j), the slopes given per query head.
 #include "common.cuh"
 
 namespace stride {
@@ -67,8 +69,8 @@ __global__ void __launch_bounds__(kWarps * 32)
 paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, const T* __restrict__ k_pages,
                                const T* __restrict__ v_pages, const int32_t* __restrict__ block_table, int table_width,
                                const int32_t* __restrict__ seq_of_token, const int32_t* __restrict__ positions, int nq,
-                               int nkv, int hd, int page_size, float scale, int window, float softcap,
-                               const float* __restrict__ sinks) {
+                               int nkv, int hd, int vd, int page_size, float scale, int window, float softcap,
+                               const float* __restrict__ sinks, const float* __restrict__ slopes) {
     pdl_trigger();
     pdl_wait();
     __shared__ __align__(16) float q_smem[kWarps][kMaxHeadDim];
@@ -76,10 +78,10 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restr
     const int t = blockIdx.x;
     const int head = blockIdx.y * kWarps + warp;
     if (head >= nq) return;
-    T* out_row = out + (static_cast<size_t>(t) * nq + head) * hd;
+    T* out_row = out + (static_cast<size_t>(t) * nq + head) * vd;
     const int seq = seq_of_token[t];
     if (seq < 0) {  // a padded token of a fixed-size batch
-        for (int d = lane; d < hd; d += 32) out_row[d] = from_f32<T>(0.f);
+        for (int d = lane; d < vd; d += 32) out_row[d] = from_f32<T>(0.f);
         return;
     }
     const int pos = positions[t];
@@ -92,6 +94,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restr
     for (int d = lane; d < hd; d += 32) qs[d] = to_f32(q_row[d]);
     __syncwarp();
 
+    const float slope = slopes ? slopes[head] : 0.f;
     float m = -INFINITY, l = 0.f;
     float acc[kMaxHeadDim / 32];
 #pragma unroll
@@ -106,6 +109,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restr
             const T* k_row = k_pages + ((static_cast<size_t>(page) * nkv + kvh) * page_size + key % page_size) * hd;
             s = dot_row<T>(qs, k_row, hd) * scale;
             if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+            if (slopes) s = __fadd_rn(s, -__fmul_rn(slope, static_cast<float>(pos - key)));
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float p = ok ? expf(s - m_new) : 0.f;
@@ -120,11 +124,11 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restr
             const float pj = __shfl_sync(0xffffffffu, p, j);
             const int kj = base + j;
             const int page = table[kj / page_size];
-            const T* v_row = v_pages + ((static_cast<size_t>(page) * nkv + kvh) * page_size + kj % page_size) * hd;
+            const T* v_row = v_pages + ((static_cast<size_t>(page) * nkv + kvh) * page_size + kj % page_size) * vd;
 #pragma unroll
             for (int i = 0; i < kMaxHeadDim / 32; ++i) {
                 const int d = lane + 32 * i;
-                if (d < hd) acc[i] = fmaf(pj, to_f32(v_row[d]), acc[i]);
+                if (d < vd) acc[i] = fmaf(pj, to_f32(v_row[d]), acc[i]);
             }
         }
         m = m_new;
@@ -141,7 +145,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restr
 #pragma unroll
     for (int i = 0; i < kMaxHeadDim / 32; ++i) {
         const int d = lane + 32 * i;
-        if (d < hd) out_row[d] = from_f32<T>(acc[i] * inv);
+        if (d < vd) out_row[d] = from_f32<T>(acc[i] * inv);
     }
 }
 
@@ -149,27 +153,27 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restr
 
 using namespace stride;
 
-// q: [tokens, q_stride] with head h at columns [h*hd, (h+1)*hd); out: [tokens, nq, hd];
-// pages: [num_pages, nkv, page_size, hd]; block_table: [seqs, table_width].
+// q: [tokens, q_stride] with head h at columns [h*hd, (h+1)*hd); out: [tokens, nq, vd];
+// key pages: [num_pages, nkv, page_size, hd], value pages the same with vd; block_table: [seqs, table_width].
 extern "C" int stride_paged_attention_generic(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                                               const int32_t* block_table, int table_width, const int32_t* seq_of_token,
-                                              const int32_t* positions, int tokens, int nq, int nkv, int hd, int page_size,
-                                              float scale, int window, float softcap, const float* sinks, int dtype,
-                                              cudaStream_t stream) {
-    if (tokens < 0 || nq <= 0 || nkv <= 0 || hd <= 0 || page_size <= 0 || table_width <= 0 || window < 0 || softcap < 0.f) return STRIDE_BAD_ARGUMENT;
+                                              const int32_t* positions, int tokens, int nq, int nkv, int hd, int vd, int page_size,
+                                              float scale, int window, float softcap, const float* sinks, const float* slopes,
+                                              int dtype, cudaStream_t stream) {
+    if (tokens < 0 || nq <= 0 || nkv <= 0 || hd <= 0 || vd <= 0 || page_size <= 0 || table_width <= 0 || window < 0 || softcap < 0.f) return STRIDE_BAD_ARGUMENT;
     if (nq % nkv) return STRIDE_BAD_ARGUMENT;
-    if (hd > kMaxHeadDim) return STRIDE_UNSUPPORTED;
+    if (hd > kMaxHeadDim || vd > kMaxHeadDim) return STRIDE_UNSUPPORTED;
     if (tokens == 0) return 0;
     dim3 grid(tokens, (nq + kWarps - 1) / kWarps);
     if (dtype == STRIDE_DTYPE_F32)
         stride::launch(paged_attention_generic_kernel<float>, dim3(grid), dim3(kWarps * 32), 0, stream, 
             static_cast<const float*>(q), q_stride, static_cast<float*>(out), static_cast<const float*>(k_pages),
-            static_cast<const float*>(v_pages), block_table, table_width, seq_of_token, positions, nq, nkv, hd, page_size, scale, window, softcap, sinks);
+            static_cast<const float*>(v_pages), block_table, table_width, seq_of_token, positions, nq, nkv, hd, vd, page_size, scale, window, softcap, sinks, slopes);
     else if (dtype == STRIDE_DTYPE_BF16)
         stride::launch(paged_attention_generic_kernel<__nv_bfloat16>, dim3(grid), dim3(kWarps * 32), 0, stream, 
             static_cast<const __nv_bfloat16*>(q), q_stride, static_cast<__nv_bfloat16*>(out),
             static_cast<const __nv_bfloat16*>(k_pages), static_cast<const __nv_bfloat16*>(v_pages), block_table, table_width,
-            seq_of_token, positions, nq, nkv, hd, page_size, scale, window, softcap, sinks);
+            seq_of_token, positions, nq, nkv, hd, vd, page_size, scale, window, softcap, sinks, slopes);
     else
         return STRIDE_BAD_ARGUMENT;
     return STRIDE_LAUNCH_STATUS();

@@ -3,13 +3,20 @@
 //   moe_route     router logits z = W_r h + b in float32 (one warp per token), the top entries (the lower index wins
 //                 among equals), and the softmax over the chosen logits only; moe_select is the choice alone, from
 //                 logits that a matrix product with float32 output has made (what the part runs);
+//   moe_select_sigmoid  the choice by another rule: scores s = sigmoid(z); choice scores c = s + correction; the experts form
+//                 equal groups of neighbours, a group's score is the sum of its two largest c, only the experts of the
+//                 `keep` best groups can be chosen (the others count as minus infinity); the `top` largest c win (the
+//                 lower index among equals); weights s / (sum of the chosen s + 1e-20) * route_scale;
 //   moe_plan      one CTA counts the rows of every expert, lays the (token, choice) pairs out expert by expert and
 //                 writes where each pair went: `offsets` [experts + 1], `perm_token` [rows] and `row_of` [tokens, top];
 //   grouped_gemm  C[p, :] = act(A[src(p), :] W[e(p)]^T) for the rows p of every expert e, the tiles of all experts in
 //                 one launch (the CTA finds its expert from `offsets` on the device, so nothing goes back to the
 //                 host and the step can be replayed from a graph); float32 FMA with a fixed k order for float32
 //                 operands, tensor-core tiles (mma_tile.cuh) for bfloat16;
-//   moe_combine   out[t] = sum_k weight[t, k] * Y[row_of[t, k]] (+ a shared expert's output), in the order of k.
+//                 act 1 squares the positive part; act 2 reads W's rows as (gate, up) pairs, row 2i beside row 2i + 1,
+//                 and writes g' sigmoid(alpha g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit), N / 2 wide;
+//   moe_combine   out[t] = sum_k weight[t, k] * Y[row_of[t, k]] (+ a shared expert's output, optionally times the
+//                 sigmoid of a per-token logit), in the order of k.
 // A row's result depends only on that row: not on the batch, nor on where the plan put it.
 #include "common.cuh"
 #include "mma_tile.cuh"
@@ -133,6 +140,113 @@ moe_select_kernel(const float* __restrict__ logits, const float* __restrict__ bi
     }
 }
 
+// logits: [tokens, ld] float32 (the first `experts` columns of a row). One warp per token.
+__global__ void __launch_bounds__(128)
+moe_select_sigmoid_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ correction,
+                          const int32_t* __restrict__ seq_of_token, int32_t* __restrict__ ids, float* __restrict__ weights, int tokens,
+                          int experts, int top, int groups, int keep, float route_scale) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float choice_s[4][kMaxExperts];
+    __shared__ float group_s[4][kMaxExperts];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= tokens) return;
+    if (seq_of_token && seq_of_token[t] < 0) {
+        for (int k = lane; k < top; k += 32) {
+            ids[static_cast<size_t>(t) * top + k] = -1;
+            weights[static_cast<size_t>(t) * top + k] = 0.f;
+        }
+        return;
+    }
+    float* choice = choice_s[warp];
+    float* gscore = group_s[warp];
+    float score[kMaxExperts / 32];       // lane holds experts lane, lane + 32, ...
+#pragma unroll
+    for (int i = 0; i < kMaxExperts / 32; ++i) {
+        const int e = i * 32 + lane;
+        score[i] = 0.f;
+        if (e < experts) {
+            score[i] = 1.f / (1.f + expf(-logits[static_cast<size_t>(t) * ld + e]));
+            choice[e] = score[i] + (correction ? correction[e] : 0.f);
+        }
+    }
+    __syncwarp();
+    if (groups > 1 && keep < groups) {
+        const int size = experts / groups;
+        for (int g = lane; g < groups; g += 32) {       // the two largest choice scores of the group
+            float a = -INFINITY, b = -INFINITY;
+            for (int e = g * size; e < (g + 1) * size; ++e) {
+                const float c = choice[e];
+                if (c > a) { b = a; a = c; }
+                else if (c > b) b = c;
+            }
+            gscore[g] = size > 1 ? a + b : a;
+        }
+        __syncwarp();
+        unsigned kept[kMaxExperts / 32] = {};           // bit l of kept[i]: group i * 32 + l stays
+        for (int k = 0; k < keep; ++k) {
+            float best = -INFINITY;
+            int best_g = 0x7fffffff;
+            for (int g = lane; g < groups; g += 32) {
+                const bool taken = (kept[g >> 5] >> (g & 31)) & 1u;
+                if (!taken && (best_g == 0x7fffffff || gscore[g] > best)) { best = gscore[g]; best_g = g; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+                if (og != 0x7fffffff && (best_g == 0x7fffffff || ob > best || (ob == best && og < best_g))) { best = ob; best_g = og; }
+            }
+            if (best_g != 0x7fffffff) kept[best_g >> 5] |= 1u << (best_g & 31);        // every lane keeps the whole set
+        }
+#pragma unroll
+        for (int i = 0; i < kMaxExperts / 32; ++i) {
+            const int e = i * 32 + lane;
+            if (e < experts) {
+                const int g = e / size;
+                if (!((kept[g >> 5] >> (g & 31)) & 1u)) choice[e] = -INFINITY;
+            }
+        }
+        __syncwarp();
+    }
+    float z[kMaxExperts / 32];
+    bool open_[kMaxExperts / 32];
+#pragma unroll
+    for (int i = 0; i < kMaxExperts / 32; ++i) {
+        const int e = i * 32 + lane;
+        open_[i] = e < experts;
+        z[i] = e < experts ? choice[e] : -INFINITY;
+    }
+    float denom = 0.f, mine = 0.f;
+    int mine_id = -1;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY, best_score = 0.f;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < kMaxExperts / 32; ++i) {
+            const int e = i * 32 + lane;
+            if (open_[i] && (best_e == 0x7fffffff || z[i] > best)) { best = z[i]; best_e = e; best_score = score[i]; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const float os = __shfl_xor_sync(0xffffffffu, best_score, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (oe != 0x7fffffff && (best_e == 0x7fffffff || ob > best || (ob == best && oe < best_e))) { best = ob; best_e = oe; best_score = os; }
+        }
+#pragma unroll
+        for (int i = 0; i < kMaxExperts / 32; ++i)
+            if (i * 32 + lane == best_e) open_[i] = false;       // taken
+        denom += best_score;
+        if (lane == k) { mine = best_score; mine_id = best_e == 0x7fffffff ? -1 : best_e; }
+    }
+    if (lane < top) {
+        ids[static_cast<size_t>(t) * top + lane] = mine_id;
+        weights[static_cast<size_t>(t) * top + lane] = mine / (denom + 1e-20f) * route_scale;
+    }
+}
+
 // ids: [tokens, top] (-1: a padded token). rank_tmp: [tokens * top] scratch.
 __global__ void __launch_bounds__(256)
 moe_plan_kernel(const int32_t* __restrict__ ids, int pairs, int experts, int32_t* __restrict__ offsets, int32_t* __restrict__ perm_token,
@@ -170,13 +284,20 @@ moe_plan_kernel(const int32_t* __restrict__ ids, int pairs, int experts, int32_t
     }
 }
 
+__device__ __forceinline__ float clamped_gated(float g, float u, float limit, float alpha) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+}
+
 // Tiles of GM x GN outputs; tile `blockIdx.y` belongs to the expert whose tiles it falls among.
 constexpr int GM = 64, GN = 64, GK = 16;
 
 template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(256)
 grouped_gemm_kernel(const TA* __restrict__ A, int lda, const int32_t* __restrict__ row_map, const TW* __restrict__ W,
-                    const int32_t* __restrict__ offsets, int experts, TC* __restrict__ C, int ldc, int N, int K, int act) {
+                    const int32_t* __restrict__ offsets, int experts, TC* __restrict__ C, int ldc, int N, int K, int act, float limit,
+                    float alpha) {
     pdl_trigger();
     pdl_wait();
     __shared__ float As[GK][GM + 4];
@@ -229,6 +350,14 @@ grouped_gemm_kernel(const TA* __restrict__ A, int lda, const int32_t* __restrict
     for (int i = 0; i < 4; ++i) {
         const int m = m0 + ty * 4 + i;
         if (m >= m_end) continue;
+        if (act == 2) {                     // columns come in (gate, up) pairs
+#pragma unroll
+            for (int j = 0; j < 4; j += 2) {
+                const int n = n0 + tx * 4 + j;
+                if (n + 1 < N) C[static_cast<size_t>(m) * ldc + n / 2] = from_f32<TC>(clamped_gated(acc[i][j], acc[i][j + 1], limit, alpha));
+            }
+            continue;
+        }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
@@ -248,7 +377,7 @@ template <typename TC>
 __global__ void __launch_bounds__(128)
 grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int32_t* __restrict__ row_map,
                        const __nv_bfloat16* __restrict__ W, const int32_t* __restrict__ offsets, int experts, TC* __restrict__ C, int ldc,
-                       int N, int K, int act) {
+                       int N, int K, int act, float limit, float alpha) {
     pdl_trigger();
     pdl_wait();
     __shared__ TileSmem sm;
@@ -280,6 +409,11 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int32
             for (int x = 0; x < 4; ++x) {
                 const int m = m0 + tile_row(i, x), n = n0 + tile_col(j, x);
                 if (m >= m_end || n >= N) continue;
+                if (act == 2) {             // elements 0 and 2 of a fragment are gates, their neighbours the ups
+                    if (!(x & 1) && n + 1 < N)
+                        C[static_cast<size_t>(m) * ldc + n / 2] = from_f32<TC>(clamped_gated(acc[i][j][x], acc[i][j][x + 1], limit, alpha));
+                    continue;
+                }
                 float v = acc[i][j][x];
                 if (act == 1) {
                     v = fmaxf(v, 0.f);
@@ -292,17 +426,19 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int32
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ Y, const int32_t* __restrict__ row_of, const float* __restrict__ weights,
-                   const T* __restrict__ shared, T* __restrict__ out, int hidden, int top) {
+                   const T* __restrict__ shared, const float* __restrict__ shared_gate, int gate_stride, T* __restrict__ out, int hidden,
+                   int top) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
+    const float share = shared_gate ? 1.f / (1.f + expf(-shared_gate[static_cast<size_t>(t) * gate_stride])) : 1.f;
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < hidden; c += gridDim.y * blockDim.x) {
         float acc = 0.f;
         for (int k = 0; k < top; ++k) {
             const int row = row_of[static_cast<size_t>(t) * top + k];
             if (row >= 0) acc = fmaf(weights[static_cast<size_t>(t) * top + k], Y[static_cast<size_t>(row) * hidden + c], acc);
         }
-        if (shared) acc += to_f32(shared[static_cast<size_t>(t) * hidden + c]);
+        if (shared) acc = fmaf(share, to_f32(shared[static_cast<size_t>(t) * hidden + c]), acc);
         out[static_cast<size_t>(t) * hidden + c] = from_f32<T>(acc);
     }
 }
@@ -350,6 +486,18 @@ int stride_moe_select(const float* logits, const float* bias, const int32_t* seq
     return STRIDE_LAUNCH_STATUS();
 }
 
+int stride_moe_select_sigmoid(const float* logits, int ld, const float* correction, const int32_t* seq_of_token, int32_t* ids,
+                              float* weights, int tokens, int experts, int top, int groups, int keep, float route_scale, cudaStream_t stream) {
+    if (tokens < 0 || experts <= 0 || top <= 0 || top > experts || ld < experts || groups <= 0 || keep <= 0 || keep > groups ||
+        experts % groups || top > keep * (experts / groups))
+        return STRIDE_BAD_ARGUMENT;
+    if (experts > kMaxExperts || top > kMaxTop) return STRIDE_UNSUPPORTED;
+    if (tokens == 0) return 0;
+    stride::launch(moe_select_sigmoid_kernel, dim3((tokens + 3) / 4), dim3(128), 0, stream, logits, ld, correction, seq_of_token, ids, weights,
+                   tokens, experts, top, groups, keep, route_scale);
+    return STRIDE_LAUNCH_STATUS();
+}
+
 int stride_moe_plan(const int32_t* ids, int tokens, int top, int experts, int32_t* offsets, int32_t* perm_token, int32_t* row_of,
                     int32_t* rank_tmp, cudaStream_t stream) {
     if (tokens < 0 || top <= 0 || experts <= 0) return STRIDE_BAD_ARGUMENT;
@@ -361,8 +509,8 @@ int stride_moe_plan(const int32_t* ids, int tokens, int top, int experts, int32_
 // kind: 0 = everything float32 (FMA); 1 = bfloat16 A and W, bfloat16 C; 2 = bfloat16 A and W, float32 C (both on the
 // tensor cores); 3 = as 2 on the FMA kernel.
 int stride_grouped_gemm(const void* A, int lda, const int32_t* row_map, const void* W, const int32_t* offsets, int experts, void* C,
-                        int ldc, int max_rows, int N, int K, int act, int kind, cudaStream_t stream) {
-    if (max_rows < 0 || experts <= 0 || N <= 0 || K <= 0 || lda < K || ldc < N) return STRIDE_BAD_ARGUMENT;
+                        int ldc, int max_rows, int N, int K, int act, float limit, float alpha, int kind, cudaStream_t stream) {
+    if (max_rows < 0 || experts <= 0 || N <= 0 || K <= 0 || lda < K || ldc < (act == 2 ? N / 2 : N) || (act == 2 && N % 2)) return STRIDE_BAD_ARGUMENT;
     if (max_rows == 0) return 0;
     const int max_tiles = (max_rows + GM - 1) / GM + experts;       // no expert has more than one ragged tile
     if (max_tiles > 65535) return STRIDE_UNSUPPORTED;
@@ -370,33 +518,33 @@ int stride_grouped_gemm(const void* A, int lda, const int32_t* row_map, const vo
     static_assert(GM == TM && GN == TN, "both forms of the grouped product use tiles of one size");
     if (kind == 1)
         stride::launch(grouped_gemm_tc_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(A), lda, row_map,
-                       static_cast<const __nv_bfloat16*>(W), offsets, experts, static_cast<__nv_bfloat16*>(C), ldc, N, K, act);
+                       static_cast<const __nv_bfloat16*>(W), offsets, experts, static_cast<__nv_bfloat16*>(C), ldc, N, K, act, limit, alpha);
     else if (kind == 2)
         stride::launch(grouped_gemm_tc_kernel<float>, grid, dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(A), lda, row_map,
-                       static_cast<const __nv_bfloat16*>(W), offsets, experts, static_cast<float*>(C), ldc, N, K, act);
+                       static_cast<const __nv_bfloat16*>(W), offsets, experts, static_cast<float*>(C), ldc, N, K, act, limit, alpha);
     else if (kind == 3)     // bfloat16 operands on the FMA kernel (kept for comparison)
         stride::launch(grouped_gemm_kernel<__nv_bfloat16, __nv_bfloat16, float>, grid, dim3(256), 0, stream,
                        static_cast<const __nv_bfloat16*>(A), lda, row_map, static_cast<const __nv_bfloat16*>(W), offsets, experts,
-                       static_cast<float*>(C), ldc, N, K, act);
+                       static_cast<float*>(C), ldc, N, K, act, limit, alpha);
     else if (kind == 0)
         stride::launch(grouped_gemm_kernel<float, float, float>, grid, dim3(256), 0, stream, static_cast<const float*>(A), lda, row_map,
-                       static_cast<const float*>(W), offsets, experts, static_cast<float*>(C), ldc, N, K, act);
+                       static_cast<const float*>(W), offsets, experts, static_cast<float*>(C), ldc, N, K, act, limit, alpha);
     else
         return STRIDE_BAD_ARGUMENT;
     return STRIDE_LAUNCH_STATUS();
 }
 
-int stride_moe_combine(const float* Y, const int32_t* row_of, const float* weights, const void* shared, void* out, int tokens, int hidden,
-                       int top, int dtype, cudaStream_t stream) {
+int stride_moe_combine(const float* Y, const int32_t* row_of, const float* weights, const void* shared, const float* shared_gate,
+                       int gate_stride, void* out, int tokens, int hidden, int top, int dtype, cudaStream_t stream) {
     if (tokens < 0 || hidden <= 0 || top <= 0) return STRIDE_BAD_ARGUMENT;
     if (tokens == 0) return 0;
     const dim3 grid(tokens, hidden >= 2048 ? 4 : 1);
     if (dtype == STRIDE_DTYPE_F32)
         stride::launch(moe_combine_kernel<float>, grid, dim3(256), 0, stream, Y, row_of, weights, static_cast<const float*>(shared),
-                       static_cast<float*>(out), hidden, top);
+                       shared_gate, gate_stride, static_cast<float*>(out), hidden, top);
     else if (dtype == STRIDE_DTYPE_BF16)
         stride::launch(moe_combine_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, Y, row_of, weights,
-                       static_cast<const __nv_bfloat16*>(shared), static_cast<__nv_bfloat16*>(out), hidden, top);
+                       static_cast<const __nv_bfloat16*>(shared), shared_gate, gate_stride, static_cast<__nv_bfloat16*>(out), hidden, top);
     else
         return STRIDE_BAD_ARGUMENT;
     return STRIDE_LAUNCH_STATUS();

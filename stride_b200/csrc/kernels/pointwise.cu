@@ -3,8 +3,12 @@
 // here), one element per thread otherwise.
 //
 //   gated_act     out = act(gate) * up for [tokens, 2 * inter] whose gate and up columns alternate in blocks
-//                 (the layout of the fused gate/up product); act: 0 SiLU, 1 the tanh form of GELU
+//                 (the layout of the fused gate/up product); act: 0 SiLU, 1 the tanh form of GELU, 2 the clamped
+//                 form g' sigmoid(a g') (u' + 1) with g' = min(g, limit) and u' = clamp(u, -limit, limit)
 //   sigmoid_gate  x *= sigmoid(g)
+//   head_gate     x[t, h, :] *= sigmoid(g[t, h]): one gate per head, read from a column block of a wider buffer
+//   add_sinusoid  x[t, 2i] += sin(p_t f_i), x[t, 2i + 1] += cos(p_t f_i) with float64 angles, and optionally the
+//                 sum's copy in the compute dtype
 //   softcap       x = c tanh(x / c)            (float32, in place: logits)
 //   tanh_inplace  x = tanh(x)
 //   weighted_sum  out = sa * a + sb * b        (the sum of two branches; out may be a or b)
@@ -51,9 +55,18 @@ __device__ __forceinline__ float act_f(float g, int act) {
     return g / (1.f + expf(-g));
 }
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+// act(gate) * up for every activation; `limit` and `alpha` only matter to the clamped form.
+__device__ __forceinline__ float gated_f(float g, float u, int act, float limit, float alpha) {
+    if (act == 2) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g * sigmoid_f(alpha * g) * (u + 1.f);
+    }
+    return act_f(g, act) * u;
+}
 
 template <typename T>
-__global__ void gated_act_vec_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, int block, int act, size_t packs) {
+__global__ void gated_act_vec_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, int block, int act, float limit, float alpha, size_t packs) {
     pdl_trigger();
     pdl_wait();
     constexpr int V = Vec<T>::V;
@@ -67,12 +80,12 @@ __global__ void gated_act_vec_kernel(const T* __restrict__ in, T* __restrict__ o
     g.load(in + at);
     u.load(in + at + block);
 #pragma unroll
-    for (int j = 0; j < V; ++j) g.v[j] = act_f(g.v[j], act) * u.v[j];
+    for (int j = 0; j < V; ++j) g.v[j] = gated_f(g.v[j], u.v[j], act, limit, alpha);
     g.store(out + t * inter + i);
 }
 
 template <typename T>
-__global__ void gated_act_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, int block, int act, size_t total) {
+__global__ void gated_act_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, int block, int act, float limit, float alpha, size_t total) {
     pdl_trigger();
     pdl_wait();
     const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
@@ -80,7 +93,7 @@ __global__ void gated_act_kernel(const T* __restrict__ in, T* __restrict__ out, 
     const size_t t = idx / inter;
     const int i = static_cast<int>(idx - t * inter);
     const size_t at = t * 2 * inter + static_cast<size_t>(i / block) * 2 * block + i % block;
-    out[idx] = from_f32<T>(act_f(to_f32(in[at]), act) * to_f32(in[at + block]));
+    out[idx] = from_f32<T>(gated_f(to_f32(in[at]), to_f32(in[at + block]), act, limit, alpha));
 }
 
 // op: 0  x *= sigmoid(g);  1  x = cap * tanh(x / cap);  2  x = tanh(x)
@@ -134,6 +147,43 @@ __global__ void weighted_sum_kernel(T* out, const T* a, float sa, const T* b, fl
     out[idx] = from_f32<T>(fmaf(sb, to_f32(b[idx]), sa * to_f32(a[idx])));
 }
 
+// x: [tokens, heads, width]; the gate of head h of token t is g[t * g_stride + h].
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ x, const T* __restrict__ g, int g_stride, int heads, int width, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    if (idx >= total) return;
+    const size_t th = idx / width;
+    const size_t t = th / heads;
+    const int h = static_cast<int>(th - t * heads);
+    x[idx] = from_f32<T>(to_f32(x[idx]) * sigmoid_f(to_f32(g[t * g_stride + h])));
+}
+
+// freq: float64 [ceil(width / 2)]. Rows of padded tokens (seq_of_token < 0) are left alone.
+template <typename T>
+__global__ void add_sinusoid_kernel(float* __restrict__ x, T* __restrict__ copy, const int32_t* __restrict__ positions,
+                                    const int32_t* __restrict__ seq_of_token, const double* __restrict__ freq, int width) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t t = blockIdx.x;
+    const bool live = seq_of_token == nullptr || seq_of_token[t] >= 0;
+    const double p = static_cast<double>(positions[t]);
+    for (int i = threadIdx.x; 2 * i < width; i += blockDim.x) {
+        double s = 0.0, c = 0.0;
+        if (live) sincos(p * freq[i], &s, &c);
+        const size_t at = t * width + 2 * i;
+        const float a = __fadd_rn(x[at], static_cast<float>(s));
+        x[at] = a;
+        if (copy) copy[at] = from_f32<T>(a);
+        if (2 * i + 1 < width) {
+            const float b = __fadd_rn(x[at + 1], static_cast<float>(c));
+            x[at + 1] = b;
+            if (copy) copy[at + 1] = from_f32<T>(b);
+        }
+    }
+}
+
 template <typename T>
 int weighted(void* out, const void* a, float sa, const void* b, float sb, long long n, cudaStream_t stream) {
     constexpr int V = Vec<T>::V;
@@ -165,17 +215,17 @@ int unary(void* x, const void* g, int op, float cap, long long n, cudaStream_t s
 }
 
 template <typename T>
-int gated(const void* in, void* out, int tokens, int inter, int block, int act, cudaStream_t stream) {
+int gated(const void* in, void* out, int tokens, int inter, int block, int act, float limit, float alpha, cudaStream_t stream) {
     constexpr int V = Vec<T>::V;
     const size_t total = static_cast<size_t>(tokens) * inter;
     const uintptr_t bits = reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out);
     if (bits % 16 == 0 && block % V == 0) {
         const size_t packs = total / V;
         stride::launch(gated_act_vec_kernel<T>, dim3(static_cast<unsigned>((packs + 127) / 128)), dim3(128), 0, stream,
-                       static_cast<const T*>(in), static_cast<T*>(out), inter, block, act, packs);
+                       static_cast<const T*>(in), static_cast<T*>(out), inter, block, act, limit, alpha, packs);
     } else {
         stride::launch(gated_act_kernel<T>, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0, stream, static_cast<const T*>(in),
-                       static_cast<T*>(out), inter, block, act, total);
+                       static_cast<T*>(out), inter, block, act, limit, alpha, total);
     }
     return STRIDE_LAUNCH_STATUS();
 }
@@ -186,13 +236,46 @@ using namespace stride;
 
 extern "C" {
 
-int stride_gated_act(const void* in, void* out, int tokens, int inter, int block, int act, int dtype, cudaStream_t stream) {
-    if (tokens < 0 || inter <= 0 || block <= 0 || inter % block || act < 0 || act > 1) return STRIDE_BAD_ARGUMENT;
+int stride_gated_act(const void* in, void* out, int tokens, int inter, int block, int act, float limit, float alpha, int dtype,
+                     cudaStream_t stream) {
+    if (tokens < 0 || inter <= 0 || block <= 0 || inter % block || act < 0 || act > 2) return STRIDE_BAD_ARGUMENT;
     if (static_cast<size_t>(tokens) * inter / 4 / 128 > 0x7fffffffull) return STRIDE_UNSUPPORTED;
     if (tokens == 0) return 0;
-    if (dtype == STRIDE_DTYPE_F32) return gated<float>(in, out, tokens, inter, block, act, stream);
-    if (dtype == STRIDE_DTYPE_BF16) return gated<__nv_bfloat16>(in, out, tokens, inter, block, act, stream);
+    if (dtype == STRIDE_DTYPE_F32) return gated<float>(in, out, tokens, inter, block, act, limit, alpha, stream);
+    if (dtype == STRIDE_DTYPE_BF16) return gated<__nv_bfloat16>(in, out, tokens, inter, block, act, limit, alpha, stream);
     return STRIDE_BAD_ARGUMENT;
+}
+
+int stride_head_gate(void* x, const void* g, int g_stride, int tokens, int heads, int width, int dtype, cudaStream_t stream) {
+    if (tokens < 0 || heads <= 0 || width <= 0 || g_stride < heads) return STRIDE_BAD_ARGUMENT;
+    const size_t total = static_cast<size_t>(tokens) * heads * width;
+    if (total / 256 > 0x7fffffffull) return STRIDE_UNSUPPORTED;
+    if (total == 0) return 0;
+    const dim3 grid(static_cast<unsigned>((total + 255) / 256));
+    if (dtype == STRIDE_DTYPE_F32)
+        stride::launch(head_gate_kernel<float>, grid, dim3(256), 0, stream, static_cast<float*>(x), static_cast<const float*>(g), g_stride,
+                       heads, width, total);
+    else if (dtype == STRIDE_DTYPE_BF16)
+        stride::launch(head_gate_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, static_cast<__nv_bfloat16*>(x),
+                       static_cast<const __nv_bfloat16*>(g), g_stride, heads, width, total);
+    else
+        return STRIDE_BAD_ARGUMENT;
+    return STRIDE_LAUNCH_STATUS();
+}
+
+int stride_add_sinusoid(float* x, void* copy, const int32_t* positions, const int32_t* seq_of_token, const double* freq, int tokens,
+                        int width, int dtype, cudaStream_t stream) {
+    if (tokens < 0 || width <= 0) return STRIDE_BAD_ARGUMENT;
+    if (tokens == 0) return 0;
+    if (dtype == STRIDE_DTYPE_F32)
+        stride::launch(add_sinusoid_kernel<float>, dim3(tokens), dim3(128), 0, stream, x, static_cast<float*>(copy), positions, seq_of_token,
+                       freq, width);
+    else if (dtype == STRIDE_DTYPE_BF16)
+        stride::launch(add_sinusoid_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), 0, stream, x, static_cast<__nv_bfloat16*>(copy), positions,
+                       seq_of_token, freq, width);
+    else
+        return STRIDE_BAD_ARGUMENT;
+    return STRIDE_LAUNCH_STATUS();
 }
 
 int stride_pointwise(void* x, const void* g, int op, float cap, long long n, int dtype, cudaStream_t stream) {

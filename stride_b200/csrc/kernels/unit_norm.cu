@@ -1,0 +1,147 @@
+// Norms whose statistic is the root mean square of a row, applied where the pre-norm decoder has none: on a sublayer's
+// output before it joins the residual stream, and on the heads of queries, keys and values before they are used or kept.
+// Statistics, scaling and the residual sum are float32; storage is float32 or bfloat16.
+//
+//   norm_add        residual[t] += m * w * y / sqrt(mean(y^2) + eps),  y = delta[t] (+ bias), and copy[t] = residual[t]
+//                   in the compute dtype (what the next sublayer's products read). Without a delta it only makes the copy.
+//   qkv_unit_norm   for every token of a fused projection [q heads | k heads | v heads | anything else]: the bias is
+//                   added, each query and key head (width hd) and each value head (width vd) is divided by its own root
+//                   mean square (no weight; either norm can be switched off), written back in place, and keys and values
+//                   go to the token's place in the pages ([page, kv_head, slot, width]) when a slot mapping is given.
+// The order of every sum depends only on the row's width, never on the batch.
+#include "common.cuh"
+
+namespace stride {
+
+template <typename T>
+__global__ void norm_add_kernel(float* __restrict__ residual, const T* __restrict__ delta, const float* __restrict__ bias,
+                                const float* __restrict__ weight, T* __restrict__ copy, int hidden, float eps, float mult) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float row_buf[];  // hidden floats, then 32 for the reduction
+    float* scratch = row_buf + hidden;
+    const size_t t = blockIdx.x;
+    float* res = residual + t * hidden;
+    if (delta == nullptr) {
+        if (copy)
+            for (int i = threadIdx.x; i < hidden; i += blockDim.x) copy[t * hidden + i] = from_f32<T>(res[i]);
+        return;
+    }
+    const T* y = delta + t * hidden;
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = to_f32(y[i]);
+        if (bias) v = __fadd_rn(v, bias[i]);
+        row_buf[i] = v;
+        sq = fmaf(v, v, sq);
+    }
+    const float total = block_sum(sq, scratch);
+    const float inv = rsqrtf(total / static_cast<float>(hidden) + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float normed = __fmul_rn(__fmul_rn(row_buf[i], inv), weight[i]);
+        const float x = __fadd_rn(res[i], __fmul_rn(mult, normed));
+        res[i] = x;
+        if (copy) copy[t * hidden + i] = from_f32<T>(x);
+    }
+}
+
+constexpr int kNormWarps = 4;
+constexpr int kMaxHead = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kNormWarps * 32)
+qkv_unit_norm_kernel(T* __restrict__ qkv, int row_stride, const float* __restrict__ bias, const int32_t* __restrict__ slot_mapping,
+                     T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv, int hd, int vd, int page_size, float eps,
+                     int norm_qk, int norm_v) {
+    pdl_trigger();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x;
+    const int head = blockIdx.y * kNormWarps + warp;          // query heads, then key heads, then value heads
+    if (head >= nq + 2 * nkv) return;
+    const bool is_value = head >= nq + nkv;
+    const int width = is_value ? vd : hd;
+    const int column = is_value ? (nq + nkv) * hd + (head - nq - nkv) * vd : head * hd;
+    T* x = qkv + static_cast<size_t>(t) * row_stride + column;
+    float v[kMaxHead / 32];
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxHead / 32; ++i) {
+        const int d = lane + 32 * i;
+        v[i] = 0.f;
+        if (d < width) {
+            v[i] = to_f32(x[d]);
+            if (bias) v[i] = __fadd_rn(v[i], bias[column + d]);
+            sq = fmaf(v[i], v[i], sq);
+        }
+    }
+    const bool normed = is_value ? norm_v != 0 : norm_qk != 0;
+    const float inv = normed ? rsqrtf(warp_sum(sq) / static_cast<float>(width) + eps) : 1.f;
+    const int slot = (slot_mapping && head >= nq) ? slot_mapping[t] : -1;
+    T* dst = nullptr;
+    if (slot >= 0) {
+        const int kvh = is_value ? head - nq - nkv : head - nq;
+        dst = (is_value ? v_pages : k_pages) + ((static_cast<size_t>(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * width;
+    }
+#pragma unroll
+    for (int i = 0; i < kMaxHead / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < width) {
+            const T out = from_f32<T>(__fmul_rn(v[i], inv));
+            x[d] = out;
+            if (dst) dst[d] = out;
+        }
+    }
+}
+
+}  // namespace stride
+
+using namespace stride;
+
+extern "C" {
+
+int stride_norm_add(float* residual, const void* delta, const float* bias, const float* weight, void* copy, int tokens, int hidden,
+                    float eps, float mult, int dtype, cudaStream_t stream) {
+    if (tokens < 0 || hidden <= 0 || (delta != nullptr && weight == nullptr)) return STRIDE_BAD_ARGUMENT;
+    if (tokens == 0) return 0;
+    const int threads = hidden >= 2048 ? 512 : hidden >= 512 ? 256 : 128;
+    const size_t smem = (static_cast<size_t>(hidden) + 32) * sizeof(float);
+    if (smem > 200 * 1024) return STRIDE_UNSUPPORTED;
+    if (dtype == STRIDE_DTYPE_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(norm_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        stride::launch(norm_add_kernel<float>, dim3(tokens), dim3(threads), smem, stream, residual, static_cast<const float*>(delta), bias,
+                       weight, static_cast<float*>(copy), hidden, eps, mult);
+    } else if (dtype == STRIDE_DTYPE_BF16) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(norm_add_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        stride::launch(norm_add_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), smem, stream, residual,
+                       static_cast<const __nv_bfloat16*>(delta), bias, weight, static_cast<__nv_bfloat16*>(copy), hidden, eps, mult);
+    } else {
+        return STRIDE_BAD_ARGUMENT;
+    }
+    return STRIDE_LAUNCH_STATUS();
+}
+
+int stride_qkv_unit_norm(void* qkv, int row_stride, const float* bias, const int32_t* slot_mapping, void* k_pages, void* v_pages,
+                         int tokens, int nq, int nkv, int hd, int vd, int page_size, float eps, int norm_qk, int norm_v, int dtype,
+                         cudaStream_t stream) {
+    if (tokens < 0 || nq < 0 || nkv < 0 || hd <= 0 || vd <= 0 || page_size <= 0 || row_stride < (nq + nkv) * hd + nkv * vd)
+        return STRIDE_BAD_ARGUMENT;
+    if (slot_mapping != nullptr && (k_pages == nullptr || v_pages == nullptr)) return STRIDE_BAD_ARGUMENT;
+    if (hd > kMaxHead || vd > kMaxHead) return STRIDE_UNSUPPORTED;
+    if (tokens == 0 || nq + nkv == 0) return 0;
+    const dim3 grid(tokens, (nq + 2 * nkv + kNormWarps - 1) / kNormWarps);
+    if (dtype == STRIDE_DTYPE_F32)
+        stride::launch(qkv_unit_norm_kernel<float>, grid, dim3(kNormWarps * 32), 0, stream, static_cast<float*>(qkv), row_stride, bias,
+                       slot_mapping, static_cast<float*>(k_pages), static_cast<float*>(v_pages), nq, nkv, hd, vd, page_size, eps, norm_qk,
+                       norm_v);
+    else if (dtype == STRIDE_DTYPE_BF16)
+        stride::launch(qkv_unit_norm_kernel<__nv_bfloat16>, grid, dim3(kNormWarps * 32), 0, stream, static_cast<__nv_bfloat16*>(qkv),
+                       row_stride, bias, slot_mapping, static_cast<__nv_bfloat16*>(k_pages), static_cast<__nv_bfloat16*>(v_pages), nq, nkv,
+                       hd, vd, page_size, eps, norm_qk, norm_v);
+    else
+        return STRIDE_BAD_ARGUMENT;
+    return STRIDE_LAUNCH_STATUS();
+}
+
+}  // extern "C"

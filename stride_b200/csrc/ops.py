@@ -40,8 +40,8 @@ _SIGNATURES = {
                                               c_int, c_void_p]),
     "stride_gemm_nt_f32": ("gemm_f32", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_paged_attention_generic": ("attention_generic", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                                                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                                                             c_int, c_float, c_void_p, c_int, c_void_p]),
+                                                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                                             c_int, c_float, c_void_p, c_void_p, c_int, c_void_p]),
     "stride_gemm_tc_skinny": ("gemm_bf16_tc", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_longlong,
                                                c_void_p, c_int, c_void_p, c_void_p]),
     "stride_gemm_tc_clustered": ("gemm_bf16_tc", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
@@ -109,11 +109,18 @@ _SIGNATURES = {
                                            c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_moe_route": ("moe", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_moe_plan": ("moe", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
-    "stride_grouped_gemm": ("moe", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                    c_void_p]),
-    "stride_moe_combine": ("moe", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "stride_grouped_gemm": ("moe", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                    c_float, c_int, c_void_p]),
+    "stride_moe_combine": ("moe", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_relu_squared": ("moe", [c_void_p, c_longlong, c_int, c_void_p]),
-    "stride_gated_act": ("pointwise", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "stride_gated_act": ("pointwise", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p]),
+    "stride_head_gate": ("pointwise", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "stride_add_sinusoid": ("pointwise", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "stride_norm_add": ("unit_norm", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p]),
+    "stride_qkv_unit_norm": ("unit_norm", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                           c_float, c_int, c_int, c_int, c_void_p]),
+    "stride_moe_select_sigmoid": ("moe", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                          c_void_p]),
     "stride_pointwise": ("pointwise", [c_void_p, c_void_p, c_int, c_float, c_longlong, c_int, c_void_p]),
     "stride_weighted_sum": ("pointwise", [c_void_p, c_void_p, c_float, c_void_p, c_float, c_longlong, c_int, c_void_p]),
     "stride_delta_prepare": ("linear_recurrence", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong,
@@ -156,7 +163,9 @@ _CLASS_OF = {
     "stride_latent_prepare": "latent norm + rotation + cache write", "stride_head_gemm": "per-head product",
     "stride_latent_attention": "attention (latent, exact kernel)", "stride_latent_attention_tc": "attention (latent, tensor cores)",
     "stride_side_gate": "token side input", "stride_side_norm_add": "token side input", "stride_cast_rows": "token side input",
-    "stride_moe_select": "router", "stride_rglru_conv": "recurrent block: convolution",
+    "stride_moe_select": "router", "stride_moe_select_sigmoid": "router", "stride_head_gate": "gates and caps",
+    "stride_add_sinusoid": "embedding", "stride_norm_add": "norm", "stride_qkv_unit_norm": "head norms + cache write",
+    "stride_rglru_conv": "recurrent block: convolution",
     "stride_rglru_gates": "recurrent block: gates", "stride_rglru_scan": "recurrent block: recurrence", "stride_rglru_scan_pieces": "recurrent block: recurrence", "stride_moe_route": "router",
     "stride_moe_plan": "router", "stride_grouped_gemm": "expert products", "stride_moe_combine": "expert sum",
     "stride_relu_squared": "relu^2", "stride_gated_act": "act * up", "stride_pointwise": "gates and caps", "stride_weighted_sum": "sum of branches",
@@ -326,16 +335,65 @@ def silu_mul(inp, out, block: int | None = None) -> None:
                                   _code(out.dtype), _stream()), "silu_mul")
 
 
-ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "swish_clamped": 2}
+EPILOGUE_ACTIVATIONS = ("silu", "gelu_tanh")      # what the gate/up products can apply in their own epilogue
 
 
-def gated_act(inp, out, block: int | None = None, activation: str = "silu") -> None:
-    """``silu_mul`` for any activation of ``ACTIVATIONS``: ``out = act(gate) * up``, same layout of ``inp``."""
+def gated_act(inp, out, block: int | None = None, activation: str = "silu", limit: float = 0.0, alpha: float = 1.0) -> None:
+    """``silu_mul`` for any activation of ``ACTIVATIONS``: ``out = act(gate) * up``, same layout of ``inp``.
+    ``swish_clamped`` is ``g' sigmoid(alpha g') (u' + 1)`` with ``g' = min(gate, limit)`` and ``u' = clamp(up, -limit, limit)``."""
     tokens, inter = out.shape
     if inp.shape != (tokens, 2 * inter) or inp.dtype != out.dtype:
         raise KernelError("gated_act wants [tokens, 2*inter] in and [tokens, inter] out of one element type")
     _check(_fn("stride_gated_act")(_dev(inp, "in"), _dev(out, "out"), tokens, inter, inter if block is None else int(block),
-                                   ACTIVATIONS[activation], _code(out.dtype), _stream()), "gated_act")
+                                   ACTIVATIONS[activation], float(limit), float(alpha), _code(out.dtype), _stream()), "gated_act")
+
+
+def head_gate(x, gates, gate_stride: int, heads: int, width: int) -> None:
+    """``x[t, h, :] *= sigmoid(gates[t * gate_stride + h])`` for ``x`` [tokens, heads * width]; ``gates`` may be a column
+    block of a wider buffer of the same element type."""
+    if x.shape[1] != heads * width or gates.dtype != x.dtype:
+        raise KernelError("head_gate: x must be [tokens, heads * width] and the gates of its element type")
+    if not gates.is_cuda:
+        raise KernelError("gates must live on a CUDA device; stride_b200 has no CPU path")
+    _check(_fn("stride_head_gate")(_dev(x, "x"), gates.data_ptr(), int(gate_stride), x.shape[0], heads, width, _code(x.dtype), _stream()),
+           "head_gate")
+
+
+def add_sinusoid(x, copy, positions, seq_of_token, freq) -> None:
+    """``x[t, 2i] += sin(p_t freq[i])``, ``x[t, 2i + 1] += cos(p_t freq[i])`` for the float32 rows ``x``; angles in float64
+    (``freq`` float64 [ceil(width / 2)]). ``copy`` (or None) receives the sums in its own element type."""
+    tokens, width = x.shape
+    if freq.dtype != torch.float64 or freq.numel() < (width + 1) // 2:
+        raise KernelError("add_sinusoid: freq must be float64 with one entry per pair of columns")
+    _check(_fn("stride_add_sinusoid")(_dev(x, "x", torch.float32), _opt(copy, "copy"), _dev(positions, "positions", torch.int32),
+                                      _opt(seq_of_token, "seq_of_token", torch.int32), _dev(freq, "freq", torch.float64), tokens, width,
+                                      _code(copy.dtype if copy is not None else torch.float32), _stream()), "add_sinusoid")
+
+
+def norm_add(residual, delta, bias, weight, copy, eps: float, mult: float) -> None:
+    """``residual += mult * weight * y / sqrt(mean(y^2) + eps)`` with ``y = delta (+ bias)`` per row, in float32; ``copy`` (or
+    None) receives the new rows in the compute dtype. ``delta`` None: only the copy is made."""
+    tokens, hidden = residual.shape
+    kind = delta if delta is not None else copy
+    if kind is None:
+        return
+    if delta is not None and copy is not None and delta.dtype != copy.dtype:
+        raise KernelError("norm_add: delta and copy must have one element type")
+    _check(_fn("stride_norm_add")(_dev(residual, "residual", torch.float32), _opt(delta, "delta"), _opt(bias, "bias", torch.float32),
+                                  _opt(weight, "weight", torch.float32), _opt(copy, "copy"), tokens, hidden, float(eps), float(mult),
+                                  _code(kind.dtype), _stream()), "norm_add")
+
+
+def qkv_unit_norm(qkv, bias, slot_mapping, k_pages, v_pages, nq: int, nkv: int, hd: int, vd: int, page_size: int, eps: float,
+                  norm_qk: bool = True, norm_v: bool = True) -> None:
+    """For the fused projection ``qkv`` [tokens, >= (nq + nkv) * hd + nkv * vd] (query heads, key heads, value heads, then
+    whatever else): adds ``bias``, divides every query and key head (and every value head) by its root mean square, in
+    place, and with ``slot_mapping`` writes keys and values into the pages. ``nkv`` 0: queries only."""
+    _check(_fn("stride_qkv_unit_norm")(_dev(qkv, "qkv"), qkv.shape[1], _opt(bias, "bias", torch.float32),
+                                       _opt(slot_mapping, "slot_mapping", torch.int32), _opt(k_pages, "k_pages", qkv.dtype),
+                                       _opt(v_pages, "v_pages", qkv.dtype), qkv.shape[0], nq, nkv, hd, vd, page_size, float(eps),
+                                       int(norm_qk), int(norm_v), _code(qkv.dtype), _stream()), "qkv_unit_norm")
 
 
 def sigmoid_gate(x, gate) -> None:
@@ -644,6 +702,16 @@ def moe_select(logits, bias, seq_of_token, ids, weights) -> None:
                                     _dev(weights, "weights", torch.float32), tokens, experts, ids.shape[1], _stream()), "moe_select")
 
 
+def moe_select_sigmoid(logits, correction, seq_of_token, ids, weights, experts: int, groups: int, keep: int, route_scale: float) -> None:
+    """From router logits (float32, the first ``experts`` columns of ``logits``' rows): scores ``sigmoid(z)``, choice scores
+    ``score + correction``, only the experts of the ``keep`` best of ``groups`` equal groups (a group's score: its two largest
+    choice scores) can be chosen, the ``top`` largest choice scores win; weights ``score / (sum + 1e-20) * route_scale``."""
+    _check(_fn("stride_moe_select_sigmoid")(_dev(logits, "logits", torch.float32), logits.shape[1], _opt(correction, "correction", torch.float32),
+                                            _opt(seq_of_token, "seq_of_token", torch.int32), _dev(ids, "ids", torch.int32),
+                                            _dev(weights, "weights", torch.float32), logits.shape[0], int(experts), ids.shape[1], int(groups),
+                                            int(keep), float(route_scale), _stream()), "moe_select_sigmoid")
+
+
 def moe_plan(ids, experts: int, offsets, perm_token, row_of, rank_tmp) -> None:
     tokens, top = ids.shape
     _check(_fn("stride_moe_plan")(_dev(ids, "ids", torch.int32), tokens, top, experts, _dev(offsets, "offsets", torch.int32),
@@ -651,9 +719,10 @@ def moe_plan(ids, experts: int, offsets, perm_token, row_of, rank_tmp) -> None:
                                   _dev(rank_tmp, "rank_tmp", torch.int32), _stream()), "moe_plan")
 
 
-def grouped_gemm(a, row_map, w, offsets, c, max_rows: int, act: int = 0) -> None:
+def grouped_gemm(a, row_map, w, offsets, c, max_rows: int, act: int = 0, limit: float = 0.0, alpha: float = 1.0) -> None:
     """For every expert e and row p in ``offsets[e] .. offsets[e+1]``: ``c[p] = act(a[row_map[p]] @ w[e].T)`` (``row_map`` None:
-    row p itself). ``w`` [experts, n, k]; ``act`` 1 squares the positive part."""
+    row p itself). ``w`` [experts, n, k]; ``act`` 1 squares the positive part; ``act`` 2 takes rows 2i and 2i + 1 of ``w[e]`` as
+    gate and up of unit i and leaves ``g' sigmoid(alpha g') (u' + 1)`` (clamped at ``limit``) in ``c`` [rows, n / 2]."""
     experts, n, k = w.shape
     if a.dtype == torch.float32:
         kind = 0
@@ -663,14 +732,19 @@ def grouped_gemm(a, row_map, w, offsets, c, max_rows: int, act: int = 0) -> None
         kind = 2
     _check(_fn("stride_grouped_gemm")(_dev(a, "a"), a.shape[1], _opt(row_map, "row_map", torch.int32), _dev(w, "w", a.dtype),
                                       _dev(offsets, "offsets", torch.int32), experts, _dev(c, "c"), c.shape[1], int(max_rows), n, k, int(act),
-                                      kind, _stream()), "grouped_gemm")
+                                      float(limit), float(alpha), kind, _stream()), "grouped_gemm")
 
 
-def moe_combine(y, row_of, weights, shared, out) -> None:
+def moe_combine(y, row_of, weights, shared, out, shared_gate=None) -> None:
+    """``shared_gate``: a float32 column (one logit per token, possibly a column of a wider buffer); the shared expert's
+    output is then multiplied by its sigmoid."""
     tokens, hidden = out.shape
+    gate_ptr, gate_stride = (None, 0) if shared_gate is None else (shared_gate.data_ptr(), shared_gate.stride(0))
+    if shared_gate is not None and (shared_gate.dtype != torch.float32 or shared_gate.shape[0] != tokens):
+        raise KernelError("moe_combine: the shared expert's gate must be one float32 logit per token")
     _check(_fn("stride_moe_combine")(_dev(y, "y", torch.float32), _dev(row_of, "row_of", torch.int32), _dev(weights, "weights", torch.float32),
-                                     _opt(shared, "shared", out.dtype), _dev(out, "out"), tokens, hidden, row_of.shape[1], _code(out.dtype),
-                                     _stream()), "moe_combine")
+                                     _opt(shared, "shared", out.dtype), gate_ptr, gate_stride, _dev(out, "out"), tokens, hidden,
+                                     row_of.shape[1], _code(out.dtype), _stream()), "moe_combine")
 
 
 def relu_squared(x) -> None:
@@ -1086,18 +1160,21 @@ def linear(x, weight, out) -> None:
 
 # -------------------------------------------------------------------- attention
 def paged_attention(q, q_stride: int, out, k_pages, v_pages, block_table, seq_of_token, positions, nq: int, nkv: int,
-                    hd: int, page_size: int, scale: float, window: int = 0, softcap: float = 0.0, sinks=None) -> None:
+                    hd: int, page_size: int, scale: float, window: int = 0, softcap: float = 0.0, sinks=None, slopes=None,
+                    vd: int | None = None) -> None:
     """Attention of every token in the flat batch over its request's pages.
     ``q`` holds head h of token t at ``q[t * q_stride + h * hd]``. ``softcap`` c > 0 caps the scaled scores at
-    c tanh(s / c); ``sinks`` (float32 [nq]) adds exp(sink) of the head to the softmax's denominator."""
+    c tanh(s / c); ``sinks`` (float32 [nq]) adds exp(sink) of the head to the softmax's denominator; ``slopes`` (float32
+    [nq]) takes slope_h times the key's distance off every score; ``vd`` is the values' width where it is not ``hd``."""
     tokens = out.shape[0]
-    if out.shape[1] != nq * hd:
-        raise KernelError("attention output has the wrong width")
+    vd = hd if vd is None else int(vd)
+    if out.shape[1] != nq * vd or k_pages.shape[-1] != hd or v_pages.shape[-1] != vd:
+        raise KernelError("attention output or pages have the wrong width")
     _check(_fn("stride_paged_attention_generic")(
         _dev(q, "q"), q_stride, _dev(out, "out"), _dev(k_pages, "k_pages"), _dev(v_pages, "v_pages"),
         _dev(block_table, "block_table", torch.int32), block_table.shape[1], _dev(seq_of_token, "seq_of_token", torch.int32),
-        _dev(positions, "positions", torch.int32), tokens, nq, nkv, hd, page_size, float(scale), int(window), float(softcap),
-        _opt(sinks, "sinks", torch.float32), _code(q.dtype), _stream()), "paged_attention")
+        _dev(positions, "positions", torch.int32), tokens, nq, nkv, hd, vd, page_size, float(scale), int(window), float(softcap),
+        _opt(sinks, "sinks", torch.float32), _opt(slopes, "slopes", torch.float32), _code(q.dtype), _stream()), "paged_attention")
 
 
 def fast_attention_supported(dtype, nq: int, nkv: int, hd: int) -> bool:

@@ -15,8 +15,18 @@ Spec params, all optional:
 * ``sinks``: a tensor ``sink`` [heads]; exp(sink_h) joins the denominator of head h's softmax.
 * ``output_gate``: a matrix ``g`` [heads * head_dim, hidden]; the concatenated heads are multiplied by
   sigmoid(g x) before the output projection.
+  ``output_gate`` ``head``: ``g`` is [heads, hidden] and gives one gate per head; its rows join the fused projection.
 * ``names`` ``short``: tensors are ``q, k, v, o`` with biases ``q.b, k.b, v.b`` under the prefix (default:
   ``q_proj.weight`` and so on).
+* ``value_dim``: the width of a value head where it is not the keys' (keys and values then lie in pages of their own width).
+* ``qk_norm`` / ``v_norm`` ``unit``: every query and key head / every value head is divided by its root mean square
+  (``norm_eps`` inside the root, no weight) after the bias and before any rotation; keys and values are kept so.
+* ``distance_slopes`` c: head h of H takes ``2^(-c (h + 1) / H) * (i - j)`` off the score of query i and key j (Press et
+  al., "Train Short, Test Long: Attention with Linear Biases Enables Input Length Extrapolation", with c = 8).
+* ``output_bias``: a bias ``o.b`` on the output projection. The mixer hands it out as ``output_bias`` and the layer's
+  arrangement adds it (the ``output_norm`` arrangement inside its norm's kernel).
+* ``borrowed_kv``: the mixer has no key and value projections and reads the pages of the cache slot it is given, which
+  another layer's mixer of the same shape writes.
 
 When the position part asks for another order of a head's entries (``head_permutation``), the rows of the query and
 key projections (and of whatever else must follow them: values taken from keys, the gate, the columns of the output
@@ -54,10 +64,33 @@ class PagedAttention(Mixer):
         self.softcap = float(p.get("softcap", 0.0))
         self.has_sinks, self.gated = bool(p.get("sinks", False)), bool(p.get("output_gate", False))
         self.short_names = p.get("names") == "short"
+        self.vd = int(p.get("value_dim", self.hd))
+        self.unit_qk, self.unit_v = p.get("qk_norm") == "unit", p.get("v_norm") == "unit"
+        self.norm_eps = float(p.get("norm_eps", 0.0))
+        self.head_gate = p.get("output_gate") == "head"
+        self.has_output_bias, self.borrows = bool(p.get("output_bias", False)), bool(p.get("borrowed_kv", False))
+        self.output_bias = None
+        if not 0 < self.vd <= 256:
+            raise ValueError(f"value_dim {self.vd} is not supported by the attention kernels (up to 256 is)")
+        if self.values_are_keys and (self.vd != self.hd or self.borrows or self.unit_qk or self.unit_v):
+            raise ValueError("values taken from keys go with neither a value width of their own, borrowed pages nor head norms")
+        # what the plain path (projection, then the position part's rotation and cache write) cannot do goes through
+        # the head-norm kernel, which adds the bias, norms and writes the pages itself when there is no rotation
+        self.plain_position = s.position is None or s.position.kind == "none"
+        self.own_prepare = self.unit_qk or self.unit_v or self.vd != self.hd or self.borrows
+        if self.own_prepare and not self.plain_position and (self.vd != self.hd or self.borrows):
+            raise ValueError("a rotation with borrowed pages or a value width of its own is not supported")
+        self.fused_gate = self.head_gate and self.own_prepare and self.plain_position
+        slope_c = p.get("distance_slopes")
+        self.slopes = None if slope_c is None else torch.tensor(
+            [2.0 ** (-float(slope_c) * (h + 1) / self.nq) for h in range(self.nq)], dtype=torch.float32, device=runtime.device)
+        self.v_dim, self.o_in = self.nkv * self.vd, self.nq * self.vd
+        self.kv_cols = 0 if self.borrows else self.kv_dim + self.v_dim
+        self.qkv_dim = self.q_dim + self.kv_cols + (self.nq if self.fused_gate else 0)
         permutation = getattr(self.position, "head_permutation", lambda: None)()
         self.perm = None if permutation is None else torch.tensor(permutation, dtype=torch.long)
         self.w_qkv = self.w_o = self.bias = self.w_gate = self.sinks = None
-        self._fast = ops.fast_attention_supported(runtime.dtype, self.nq, self.nkv, self.hd)
+        self._fast = ops.fast_attention_supported(runtime.dtype, self.nq, self.nkv, self.hd) and self.vd == self.hd and self.slopes is None
         self.accepts_folded = not self.gated          # the gate reads the normed input as a tensor
 
     # ----------------------------------------------------------------- weights
@@ -68,21 +101,26 @@ class PagedAttention(Mixer):
         else:
             w, b = {k: f"{p}{k}_proj.weight" for k in "qkvo"}, {k: f"{p}{k}_proj.bias" for k in "qkv"}
         w["g"], w["sink"] = p + "g", p + "sink"
+        b["o"] = f"{p}o.b" if self.short_names else f"{p}o_proj.bias"
         return w, b
 
     def declare(self):
         w, b = self._names()
-        d = {w["q"]: TensorDecl((self.q_dim, self.hidden)), w["k"]: TensorDecl((self.kv_dim, self.hidden)),
-             w["o"]: TensorDecl((self.hidden, self.q_dim))}
-        if not self.values_are_keys:
-            d[w["v"]] = TensorDecl((self.kv_dim, self.hidden))
+        d = {w["q"]: TensorDecl((self.q_dim, self.hidden)), w["o"]: TensorDecl((self.hidden, self.o_in))}
+        if not self.borrows:
+            d[w["k"]] = TensorDecl((self.kv_dim, self.hidden))
+            if not self.values_are_keys:
+                d[w["v"]] = TensorDecl((self.v_dim, self.hidden))
         if self.spec.bias:
             d[b["q"]] = TensorDecl((self.q_dim,), "vector")
-            d[b["k"]] = TensorDecl((self.kv_dim,), "vector")
-            if not self.values_are_keys:
-                d[b["v"]] = TensorDecl((self.kv_dim,), "vector")
+            if not self.borrows:
+                d[b["k"]] = TensorDecl((self.kv_dim,), "vector")
+                if not self.values_are_keys:
+                    d[b["v"]] = TensorDecl((self.v_dim,), "vector")
+        if self.has_output_bias:
+            d[b["o"]] = TensorDecl((self.hidden,), "vector")
         if self.gated:
-            d[w["g"]] = TensorDecl((self.q_dim, self.hidden))
+            d[w["g"]] = TensorDecl((self.nq if self.head_gate else self.q_dim, self.hidden))
         if self.has_sinks:
             d[w["sink"]] = TensorDecl((self.nq,), "vector")
         d.update(self.position.declare())          # a position encoding may have tensors of its own
@@ -99,9 +137,13 @@ class PagedAttention(Mixer):
 
     def bind(self, weights):
         w, b = self._names()
+        if self.own_prepare:
+            return self._bind_own(weights, w, b)
         q, k = self._reorder(weights[w["q"]]), self._reorder(weights[w["k"]])
         v = k if self.values_are_keys else weights[w["v"]]
         self.w_qkv = torch.cat([q, k, v], dim=0).contiguous()
+        if self.has_output_bias:
+            self.output_bias = weights[b["o"]]
         # values taken from keys come in the keys' order, and so do the heads' outputs
         self.w_o = self._reorder(weights[w["o"]], dim=1) if self.values_are_keys else weights[w["o"]]
         if self.spec.bias:
@@ -113,7 +155,45 @@ class PagedAttention(Mixer):
             self.sinks = weights[w["sink"]]
         self.position.bind(weights)
 
+    def _bind_own(self, weights, w, b):
+        """The fused projection of the head-norm path: query rows, then key and value rows unless they are borrowed,
+        then the rows of a per-head gate. No reordering: a rotation that wants one is not combined with this path."""
+        if self.perm is not None:
+            raise ValueError("head norms are not combined with a rotation that reorders the heads' entries")
+        order = ["q"] + ([] if self.borrows else ["k", "v"])
+        rows = [weights[w[n]] for n in order] + ([weights[w["g"]]] if self.fused_gate else [])
+        self.w_qkv = torch.cat(rows, dim=0).contiguous()
+        self.w_o = weights[w["o"]]
+        if self.spec.bias:
+            self.bias = torch.cat([weights[b[n]] for n in order]).contiguous()
+        if self.gated and not self.fused_gate:
+            self.w_gate = weights[w["g"]]
+        if self.has_sinks:
+            self.sinks = weights[w["sink"]]
+        if self.has_output_bias:
+            self.output_bias = weights[b["o"]]
+        self.position.bind(weights)
+
+    def _named_own(self):
+        w, b = self._names()
+        out, at = {w["o"]: self.w_o}, 0
+        for n, rows in [("q", self.q_dim)] + ([] if self.borrows else [("k", self.kv_dim), ("v", self.v_dim)]):
+            out[w[n]] = self.w_qkv[at:at + rows]
+            if self.bias is not None:
+                out[b[n]] = self.bias[at:at + rows]
+            at += rows
+        if self.gated:
+            out[w["g"]] = self.w_qkv[at:at + self.nq] if self.fused_gate else self.w_gate
+        if self.has_sinks:
+            out[w["sink"]] = self.sinks
+        if self.has_output_bias:
+            out[b["o"]] = self.output_bias
+        out.update(self.position.named_tensors())
+        return out
+
     def named_tensors(self):
+        if self.own_prepare:
+            return self._named_own()
         w, b = self._names()
         q, k = self.q_dim, self.q_dim + self.kv_dim
         back = lambda t, dim=0: self._reorder(t, inverse=True, dim=dim)
@@ -129,11 +209,15 @@ class PagedAttention(Mixer):
             out[w["g"]] = back(self.w_gate) if self.values_are_keys else self.w_gate
         if self.has_sinks:
             out[w["sink"]] = self.sinks
+        if self.has_output_bias:
+            out[b["o"]] = self.output_bias
         out.update(self.position.named_tensors())
         return out
 
     # ------------------------------------------------------------------- cache
     def cache_request(self):
+        if self.vd != self.hd:
+            return CacheRequest(window=self.spec.window, tensors=(("k", self.nkv, self.hd), ("v", self.nkv, self.vd)))
         return CacheRequest(self.nkv, self.hd, self.spec.window)
 
     # ----------------------------------------------------------------- forward
@@ -144,14 +228,25 @@ class PagedAttention(Mixer):
         tokens = x.shape[0]
         qkv = self.rt.buffer("qkv", tokens, self.qkv_dim)
         folded = x if isinstance(x, ops.FoldedNorm) else None
-        if not self._project_and_rotate(folded.xt if folded else x, qkv, ctx, cache, tokens, folded):
+        if self.own_prepare:
+            if folded:
+                x = folded.tensor()
+            ops.linear(x, self.w_qkv, qkv)
+            self._norm_and_store(qkv, ctx, cache, tokens)
+        elif not self._project_and_rotate(folded.xt if folded else x, qkv, ctx, cache, tokens, folded):
             if folded:
                 x = folded.tensor()
             ops.linear(x, self.w_qkv, qkv)
             self.position.encode_and_store(qkv, self.bias, ctx, cache, self.nq, self.nkv, self.hd)
-        attn = self.rt.buffer("attn", tokens, self.q_dim)
+        attn = self.rt.buffer("attn", tokens, self.o_in)
         self._attend(qkv, attn, ctx, cache, tokens)
-        if self.gated:
+        if self.fused_gate:
+            ops.head_gate(attn, qkv[:, self.q_dim + self.kv_cols:], self.qkv_dim, self.nq, self.vd)
+        elif self.head_gate:
+            gate = self.rt.buffer("attn_gate", tokens, self.nq)
+            ops.linear(x, self.w_gate, gate)
+            ops.head_gate(attn, gate, self.nq, self.nq, self.vd)
+        elif self.gated:
             gate = self.rt.buffer("attn_gate", tokens, self.q_dim)
             ops.linear(x, self.w_gate, gate)
             ops.sigmoid_gate(attn, gate)
@@ -161,6 +256,20 @@ class PagedAttention(Mixer):
         ops.linear(attn, self.w_o, out)
         return out
 
+
+    def _norm_and_store(self, qkv, ctx, cache, tokens):
+        """Bias, head norms and the pages: in one kernel when there is no rotation, else the norms here and rotation and
+        pages through the position part."""
+        writes = cache.writes and not self.borrows
+        nkv = 0 if self.borrows else self.nkv
+        if self.plain_position:
+            slots = ctx.slot_mapping[cache.group][:tokens] if writes else None
+            ops.qkv_unit_norm(qkv, self.bias, slots, cache.k_pages if writes else None, cache.v_pages if writes else None, self.nq, nkv,
+                              self.hd, self.vd, cache.page_size, self.norm_eps, self.unit_qk, self.unit_v)
+        else:
+            ops.qkv_unit_norm(qkv, self.bias, None, None, None, self.nq, nkv, self.hd, self.vd, cache.page_size, self.norm_eps,
+                              self.unit_qk, self.unit_v)
+            self.position.encode_and_store(qkv, None, ctx, cache, self.nq, self.nkv, self.hd)
 
     def _project_and_rotate(self, x, qkv, ctx, cache, tokens, folded=None) -> bool:
         """A decode step's projection with the position encoding and the cache write in its epilogue, when the
@@ -185,7 +294,7 @@ class PagedAttention(Mixer):
         if not self._fast:
             # the exact kernel: the whole 32-bit path, and bfloat16 sizes the tensor-core kernels refuse
             ops.paged_attention(qkv, self.qkv_dim, attn, cache.k_pages, cache.v_pages, table, ctx.seq_of_token[:tokens],
-                                ctx.positions[:tokens], *geometry, self.softcap, self.sinks)
+                                ctx.positions[:tokens], *geometry, self.softcap, self.sinks, self.slopes, self.vd)
             return
         split = min(ctx.decode_tail_start, tokens)          # portions before, single decoded tokens after
         if split > 0:

@@ -135,6 +135,11 @@ class Norm(Part):
         (int32 indices) only those rows are produced, into ``out[i]``, and ``residual`` stays as it is."""
         raise NotImplementedError
 
+    def add_normed(self, residual, delta, bias, mult: float, copy) -> None:
+        """For an arrangement that norms a sublayer's output: ``residual += mult * norm(delta + bias)`` in float32
+        (``bias``: float32 [hidden] or None), and ``copy`` (compute dtype, or None) receives the new rows. Optional."""
+        raise NotImplementedError(f"the norm {type(self).__name__} cannot sit on a sublayer's output")
+
 
 class PositionEncoding(Part):
     def encode_and_store(self, qkv, bias, ctx, cache, num_heads: int, num_kv_heads: int, head_dim: int) -> None:

@@ -2,7 +2,11 @@
 each read a normed copy of the residual stream and add their output back
 (python/stride_worker/model.py:254-310). The spec may put a multiplier on every
 sum into the stream, leave the feed-forward out, and name parts that add a
-token-dependent input to the stream after the feed-forward."""
+token-dependent input to the stream after the feed-forward.
+
+``output_norm``: the sublayers read the stream itself and the norm sits on what they give back,
+``x += m * norm(mixer(x)); x += m * norm(ffn(x))``. A sublayer's last bias (``output_bias``) is added inside the
+norm's kernel."""
 
 from __future__ import annotations
 
@@ -10,6 +14,8 @@ from .base import Layer, build_part, register_part
 
 
 class PreNormLayer(Layer):
+    adds_output_bias = False
+
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.mixer_norm = build_part("norm", spec.mixer_norm, runtime)
@@ -19,6 +25,8 @@ class PreNormLayer(Layer):
         self.feed_forward = build_part("feed_forward", spec.feed_forward, runtime) if has_ffn else None
         self.after = tuple(build_part("stream_input", s, runtime) for s in getattr(spec, "after", ()))
         self.mult = float(getattr(spec, "residual_mult", 1.0))
+        if not self.adds_output_bias and any(getattr(p, "has_output_bias", False) for p in (self.mixer, self.feed_forward)):
+            raise ValueError(f"the arrangement {spec.kind!r} does not add a sublayer's output bias")
 
     def parts(self):
         own = (self.mixer_norm, self.mixer) + ((self.ffn_norm, self.feed_forward) if self.feed_forward is not None else ())
@@ -53,4 +61,18 @@ class PreNormLayer(Layer):
             part.forward(stream, ctx, mult)
 
 
+class OutputNormLayer(PreNormLayer):
+    """The same parts in the other arrangement: no norm before a sublayer, one on its output."""
+    adds_output_bias = True
+
+    def forward(self, stream, ctx, cache):
+        mixer, ffn, mult = self.mixer, self.feed_forward, self.mult
+        stream.add_normed(mixer.forward(stream.values(), ctx, cache), self.mixer_norm, mult, getattr(mixer, "output_bias", None))
+        if ffn is not None:
+            stream.add_normed(ffn.forward(stream.values(), ctx), self.ffn_norm, mult, getattr(ffn, "output_bias", None))
+        for part in self.after:
+            part.forward(stream, ctx, mult)
+
+
 register_part("layer", "pre_norm", PreNormLayer)
+register_part("layer", "output_norm", OutputNormLayer)

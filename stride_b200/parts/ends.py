@@ -4,7 +4,9 @@
 (python/stride_worker/model.py:250-252). ``linear``: logits are the normed rows times the head matrix, computed in
 the compute dtype and returned in float32; a head whose spec names no tensor shares the embedding table
 (python/stride_worker/model.py:127-130, 322-341). An architecture that scales its embedding, adds a bias to its
-head registers another kind; the model itself does not change. A ``linear`` head whose spec gives the param
+head registers another kind; the model itself does not change. ``lookup`` with the param ``sinusoid`` b adds the fixed
+position vector of Vaswani et al., "Attention Is All You Need", in neighbouring pairs: entry 2i gets sin(p b^(-2i / hidden)),
+entry 2i + 1 the cosine of the same angle, formed in float64 on the device. A ``linear`` head whose spec gives the param
 ``softcap`` c caps its logits at c tanh(logits / c).
 """
 
@@ -18,6 +20,12 @@ class LookupEmbedding(Embedding):
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.weight = None
+        base = dict(spec.params).get("sinusoid")
+        self.freq = None
+        if base:
+            import torch
+            pairs = torch.arange((spec.hidden + 1) // 2, dtype=torch.float64)
+            self.freq = (float(base) ** (-2.0 * pairs / spec.hidden)).to(runtime.device)
 
     def declare(self):
         return {self.spec.name: TensorDecl((self.spec.vocab, self.spec.hidden))}
@@ -34,6 +42,8 @@ class LookupEmbedding(Embedding):
     def forward(self, ctx, out):
         tokens = out.shape[0]
         ops.embed_gather(ctx.token_ids[:tokens], ctx.seq_of_token[:tokens], self.weight, out)
+        if self.freq is not None:
+            ops.add_sinusoid(out, None, ctx.positions[:tokens], ctx.seq_of_token[:tokens], self.freq)
 
 
 class LinearHead(Head):

@@ -2,7 +2,12 @@
 multiplying after the normalisation (python/stride_worker/layers.py:24-35).
 
 Spec params: ``tensor`` names the weight (default: the prefix + ``weight``); ``weight_offset`` c makes the factor
-``c + w`` for checkpoints that keep w = factor - c (the sum is formed once, in float32, when the weight is bound)."""
+``c + w`` for checkpoints that keep w = factor - c (the sum is formed once, in float32, when the weight is bound);
+``shape`` ``scalar``: the checkpoint keeps one number for all coordinates (a tensor without dimensions), which is spread
+over the width when it is bound, so every kernel sees a vector.
+
+Besides the pre-norm use (``apply``) the norm can sit on a sublayer's output: ``add_normed`` adds ``mult * norm(delta)``
+to the residual stream."""
 
 from __future__ import annotations
 
@@ -19,14 +24,16 @@ class RMSNorm(Norm):
         p = dict(spec.params)
         self._name = p.get("tensor", spec.prefix + "weight")
         self.offset = float(p.get("weight_offset", 0.0))
+        self.scalar = p.get("shape") == "scalar"
         self.stored = None
 
     def declare(self):
-        return {self._name: TensorDecl((self.width,), "vector")}
+        return {self._name: TensorDecl(() if self.scalar else (self.width,), "vector")}
 
     def bind(self, weights):
         self.stored = weights[self._name]
-        self.weight = self.stored + self.offset if self.offset else self.stored
+        weight = self.stored.reshape(1).expand(self.width).contiguous() if self.scalar else self.stored
+        self.weight = weight + self.offset if self.offset else weight
 
     def named_tensors(self):
         return {self._name: self.stored}
@@ -36,6 +43,9 @@ class RMSNorm(Norm):
 
     def apply(self, residual, pending, out, rows=None):
         ops.add_rmsnorm(residual, pending, self.weight, out, self.eps, rows=rows)      # sum, write-back and norm in one kernel
+
+    def add_normed(self, residual, delta, bias, mult, copy):
+        ops.norm_add(residual, delta, bias, self.weight, copy, self.eps, mult)         # norm, sum, write-back and copy in one kernel
 
 
 register_part("norm", "rmsnorm", RMSNorm)

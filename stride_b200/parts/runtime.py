@@ -77,6 +77,27 @@ class ResidualStream:
         self.residual = runtime.buffer("residual", tokens, hidden, torch.float32)
         self._pending = None
         self._scale = 1.0
+        self._copy_valid = False        # the compute-dtype copy of the stream is up to date
+
+    def values(self):
+        """The stream itself in the compute dtype, for a sublayer that reads it without a norm in between: the
+        float32 rows in a float32 model, else a copy that ``add_normed`` keeps up to date."""
+        self._settle()
+        if self.rt.dtype == torch.float32:
+            return self.residual
+        copy = self.rt.buffer("stream_copy", self.tokens, self.hidden)
+        if not self._copy_valid:
+            ops.norm_add(self.residual, None, None, None, copy, 0.0, 0.0)
+            self._copy_valid = True
+        return copy
+
+    def add_normed(self, delta, norm, scale: float = 1.0, bias=None) -> None:
+        """``stream += scale * norm(delta + bias)``: the sum for layers that norm a sublayer's output. One kernel, which
+        also refreshes the copy that ``values`` hands out."""
+        self._settle()
+        copy = None if self.rt.dtype == torch.float32 else self.rt.buffer("stream_copy", self.tokens, self.hidden)
+        norm.add_normed(self.residual, self._run(delta), bias, float(scale), copy)
+        self._copy_valid = copy is not None
 
     def add(self, delta, scale: float = 1.0) -> None:
         """``delta``: a tensor, or a ``Projection`` (a product not yet run) that the next ``normed`` may fold. The
@@ -84,6 +105,7 @@ class ResidualStream:
         self._settle()
         self._pending = delta
         self._scale = float(scale)
+        self._copy_valid = False
 
     def _settle(self) -> None:
         """Applies what is pending to the residual."""
@@ -168,6 +190,7 @@ class ResidualStream:
         return ops.FoldedNorm(xt, partials, count, eps, lambda: self.rt.buffer(tag, self.tokens, self.hidden), stride)
 
     def materialize(self):
-        """The stream with every pending sum applied (float32)."""
+        """The stream with every pending sum applied (float32). The caller may add to it."""
         self._settle()
+        self._copy_valid = False
         return self.residual

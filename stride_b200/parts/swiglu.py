@@ -1,5 +1,6 @@
 """Dense gated feed-forward: ``down(act(gate(x)) * up(x))``, act SiLU or the tanh form of GELU
-(python/stride_worker/layers.py:152-161). Gate and up are one matrix product
+(python/stride_worker/layers.py:152-161), or the clamped form ``swish_clamped``: ``g' sigmoid(alpha g') (u' + 1)`` with
+``g' = min(gate(x), limit)`` and ``u' = clamp(up(x), -limit, limit)`` (spec params ``limit`` and ``alpha``). Gate and up are one matrix product
 (their weights are stacked at load time); SiLU and the product run in float32.
 
 In bfloat16, when the inner width allows it, the stacked weight alternates 64 rows
@@ -29,6 +30,9 @@ class SwiGLU(FeedForward):
             raise ValueError(f"activation {spec.activation!r} is not supported by the gated feed-forward (one of {sorted(ops.ACTIVATIONS)} is)")
         self.activation = spec.activation
         self.short_names = dict(spec.params).get("names") == "short"
+        self.limit, self.alpha = float(dict(spec.params).get("limit", 0.0)), float(dict(spec.params).get("alpha", 1.0))
+        if self.activation == "swish_clamped" and not self.limit > 0:
+            raise ValueError("the clamped activation needs a positive `limit`")
         self.hidden, self.inter = spec.hidden, spec.intermediate
         self.w_gate_up = self.w_down = None
 
@@ -63,7 +67,7 @@ class SwiGLU(FeedForward):
         act = self.rt.buffer("ffn_act", tokens, self.inter)
         folded = x if isinstance(x, ops.FoldedNorm) else None
         # the tcgen05 product for a few tokens applies either activation in its epilogue, the tokens-as-rows product SiLU only
-        gated = self.block == ops.GATED_BLOCK and (
+        gated = self.block == ops.GATED_BLOCK and self.activation in ops.EPILOGUE_ACTIVATIONS and (
             ops.linear_gated_tc(folded.xt if folded else x, self.w_gate_up, act, folded, self.activation)
             or (self.activation == "silu" and ops.rows_wanted(tokens)
                 and ops.linear_rows_gated(folded.xt if folded else x, self.w_gate_up, act, folded)))
@@ -75,7 +79,7 @@ class SwiGLU(FeedForward):
             if self.activation == "silu":
                 ops.silu_mul(gate_up, act, self.block)
             else:
-                ops.gated_act(gate_up, act, self.block, self.activation)
+                ops.gated_act(gate_up, act, self.block, self.activation, self.limit, self.alpha)
         if lazy_output:
             return Projection(act, self.w_down)        # the residual stream runs it, with the sum and norm that follow if it can
         out = self.rt.buffer("ffn_out", tokens, self.hidden)
