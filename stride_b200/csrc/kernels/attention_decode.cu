@@ -48,7 +48,7 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
                           int table_width, const int32_t* __restrict__ seq_of_token, const int32_t* __restrict__ positions,
                           float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ tickets,
                           __nv_bfloat16* __restrict__ out, int nq, int nkv, int page_size, float scale_log2e, int window,
-                          float cap_in, const float* __restrict__ sinks,
+                          float cap_in, const float* __restrict__ sinks, const float* __restrict__ slopes,
                           int split_keys, int num_splits, int* __restrict__ status) {
     pdl_trigger();
     // The step's index arrays and the keys of earlier steps are not written by the kernels before this one.
@@ -93,6 +93,12 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tg = lane & 3;
+    float slope_raw[2] = {0.f, 0.f};      // of the heads in rows g and g + 8 of the tile, in the units of the raw scores
+    if (slopes != nullptr) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+            if (g + 8 * r < group) slope_raw[r] = slopes[kvh * group + g + 8 * r] * 1.4426950408889634f / scale_log2e;
+    }
     const int32_t* table = block_table + static_cast<size_t>(seq) * table_width;
     const int n_tiles = split_keys / kGroupKeys;          // tiles this warp walks: tile j holds keys base(j) .. +15
     auto tile_base = [&](int j) { return lo + j * kGroupKeys + warp * kTileKeys; };
@@ -235,6 +241,13 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
                 for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) s[nt][e] = tanh_approx(s[nt][e] * cap_in);
+            }
+            if (slopes != nullptr) {    // a penalty on the key's distance; a row of the tile is a head of the group
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        s[nt][e] = fmaf(slope_raw[e >> 1], static_cast<float>(tlo + nt * 8 + 2 * tg + (e & 1) - pos), s[nt][e]);
             }
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -444,8 +457,8 @@ template <int HD>
 int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, const __nv_bfloat16* k_pages,
                   const __nv_bfloat16* v_pages, long long cache_rows, const int32_t* block_table, int table_width,
                   const int32_t* seq_of_token, const int32_t* positions, float* part_o, float* part_ml, int* tickets, int tokens,
-                  int nq, int nkv, int page_size, float scale, int window, float softcap, const float* sinks, int split_keys,
-                  int num_splits, int* status, cudaStream_t stream) {
+                  int nq, int nkv, int page_size, float scale, int window, float softcap, const float* sinks, const float* slopes,
+                  int split_keys, int num_splits, int* status, cudaStream_t stream) {
     constexpr int smem = kStages * 4 * 2 * kTileKeys * HD * 2 + 1024;      // the rings, and room to align them to 1024 bytes
     // the merge keeps one weight per (head of the group, split) and one sum per head in the tile ring's memory
     if (static_cast<long long>(nq / nkv) * (num_splits + 1) * 4 > smem - 1024) return STRIDE_UNSUPPORTED;
@@ -473,12 +486,12 @@ int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, cons
     if (tma)
         stride::launch(paged_decode_split_kernel<HD, true>, grid, dim3(128), smem, stream, *map_k, *map_v, q, q_stride, k_pages, v_pages,
                        block_table, table_width, seq_of_token, positions, part_o, part_ml, tickets, out, nq, nkv, page_size,
-                       (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, window, softcap > 0.f ? scale / softcap : 0.f, sinks,
+                       (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, window, softcap > 0.f ? scale / softcap : 0.f, sinks, slopes,
                        split_keys, num_splits, status);
     else
         stride::launch(paged_decode_split_kernel<HD, false>, grid, dim3(128), smem, stream, no_map, no_map, q, q_stride, k_pages, v_pages,
                        block_table, table_width, seq_of_token, positions, part_o, part_ml, tickets, out, nq, nkv, page_size,
-                       (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, window, softcap > 0.f ? scale / softcap : 0.f, sinks,
+                       (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, window, softcap > 0.f ? scale / softcap : 0.f, sinks, slopes,
                        split_keys, num_splits, status);
     return STRIDE_LAUNCH_STATUS();
 }
@@ -511,12 +524,13 @@ int stride_paged_decode_attention_tma(const void* q, int q_stride, void* out, co
                                       cudaStream_t stream);
 
 // The same with a cap c > 0 on the scaled scores, c tanh(s / c) (the hardware's tanh), and with sinks (float32 [nq] or
-// null): exp(sink) of the head joins the softmax's denominator.
+// null): exp(sink) of the head joins the softmax's denominator; and with slopes (float32 [nq] or null): head h takes
+// slope_h times the key's distance off every score.
 int stride_paged_decode_attention_rules(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                                         int num_pages, const int32_t* block_table, int table_width, const int32_t* seq_of_token,
                                         const int32_t* positions, float* scratch, long long scratch_floats, int tokens, int nq,
                                         int nkv, int hd, int page_size, float scale, int window, float softcap, const float* sinks,
-                                        int max_context, int* status, cudaStream_t stream);
+                                        const float* slopes, int max_context, int* status, cudaStream_t stream);
 
 // The same without the two things the TMA copies need (the number of pages and a status word): cp.async copies.
 int stride_paged_decode_attention(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
@@ -538,14 +552,14 @@ int stride_paged_decode_attention_tma(const void* q, int q_stride, void* out, co
                                       cudaStream_t stream) {
     return stride_paged_decode_attention_rules(q, q_stride, out, k_pages, v_pages, num_pages, block_table, table_width, seq_of_token,
                                                positions, scratch, scratch_floats, tokens, nq, nkv, hd, page_size, scale, window, 0.f,
-                                               nullptr, max_context, status, stream);
+                                               nullptr, nullptr, max_context, status, stream);
 }
 
 int stride_paged_decode_attention_rules(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                                         int num_pages, const int32_t* block_table, int table_width, const int32_t* seq_of_token,
                                         const int32_t* positions, float* scratch, long long scratch_floats, int tokens, int nq,
                                         int nkv, int hd, int page_size, float scale, int window, float softcap, const float* sinks,
-                                        int max_context, int* status, cudaStream_t stream) {
+                                        const float* slopes, int max_context, int* status, cudaStream_t stream) {
     if (softcap < 0.f) return STRIDE_BAD_ARGUMENT;
     if (tokens < 0 || nq <= 0 || nkv <= 0 || page_size <= 0 || table_width <= 0 || window < 0 || max_context <= 0)
         return STRIDE_BAD_ARGUMENT;
@@ -568,9 +582,9 @@ int stride_paged_decode_attention_rules(const void* q, int q_stride, void* out, 
     const long long cache_rows = static_cast<long long>(num_pages) * nkv * page_size;
     if (hd == 64)
         return launch_decode<64>(qp, q_stride, op, kp, vp, cache_rows, block_table, table_width, seq_of_token, positions, part_o,
-                                 part_ml, tickets, tokens, nq, nkv, page_size, scale, window, softcap, sinks, split_keys, num_splits, status, stream);
+                                 part_ml, tickets, tokens, nq, nkv, page_size, scale, window, softcap, sinks, slopes, split_keys, num_splits, status, stream);
     return launch_decode<128>(qp, q_stride, op, kp, vp, cache_rows, block_table, table_width, seq_of_token, positions, part_o,
-                              part_ml, tickets, tokens, nq, nkv, page_size, scale, window, softcap, sinks, split_keys, num_splits, status, stream);
+                              part_ml, tickets, tokens, nq, nkv, page_size, scale, window, softcap, sinks, slopes, split_keys, num_splits, status, stream);
 }
 
 }  // extern "C"

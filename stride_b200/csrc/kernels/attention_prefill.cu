@@ -25,7 +25,8 @@ paged_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfl
                      const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
                      const int32_t* __restrict__ block_table, int table_width, const int32_t* __restrict__ q_start,
                      const int32_t* __restrict__ q_len, const int32_t* __restrict__ ctx_len, int num_seqs, int nq, int nkv,
-                     int page_size, float scale_log2e, int window, float cap_in, const float* __restrict__ sinks) {
+                     int page_size, float scale_log2e, int window, float cap_in, const float* __restrict__ sinks,
+                     const float* __restrict__ slopes) {
     pdl_trigger();
     pdl_wait();
     constexpr int ROW_BYTES = HD * 2;
@@ -146,6 +147,16 @@ paged_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfl
 #pragma unroll
                 for (int e = 0; e < 4; ++e) s[nt][e] = tanh_approx(s[nt][e] * cap_in);
         }
+        if (slopes != nullptr) {    // a penalty on the key's distance, in the units of the raw scores
+            const float slope_raw = slopes[head] * 1.4426950408889634f / scale_log2e;
+#pragma unroll
+            for (int nt = 0; nt < kKTile / 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = k0 + nt * 8 + 2 * tg + (e & 1);
+                    s[nt][e] = fmaf(slope_raw, static_cast<float>(key - ((e >> 1) ? pos_b : pos_a)), s[nt][e]);
+                }
+        }
         float mx[2] = {-INFINITY, -INFINITY};
         // Only tiles that touch the diagonal or the window's edge need the mask.
         const int warp_first_pos = pos0 + min(wr0, rows - 1);
@@ -238,7 +249,7 @@ template <int HD>
 int launch_prefill(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, const __nv_bfloat16* k_pages,
                    const __nv_bfloat16* v_pages, const int32_t* block_table, int table_width, const int32_t* q_start,
                    const int32_t* q_len, const int32_t* ctx_len, int num_seqs, int max_tiles, int nq, int nkv, int page_size,
-                   float scale, int window, float softcap, const float* sinks, cudaStream_t stream) {
+                   float scale, int window, float softcap, const float* sinks, const float* slopes, cudaStream_t stream) {
     const int smem = 2 * 2 * kKTile * HD * 2;
     static bool configured = false;
     if (!configured) {
@@ -250,7 +261,7 @@ int launch_prefill(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, con
     stride::launch(paged_prefill_kernel<HD>, dim3(grid), dim3(128), smem, stream, q, q_stride, out, k_pages, v_pages, block_table, table_width, q_start,
                                                           q_len, ctx_len, num_seqs, nq, nkv, page_size,
                                                           (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, window,
-                                                          softcap > 0.f ? scale / softcap : 0.f, sinks);
+                                                          softcap > 0.f ? scale / softcap : 0.f, sinks, slopes);
     return STRIDE_LAUNCH_STATUS();
 }
 
@@ -262,12 +273,13 @@ using namespace stride;
 // `tokens` rows of the flat batch. q: [tokens, q_stride]; out: [tokens, nq * hd].
 // Returns -2 for sizes it does not run (head sizes other than 64 and 128); the
 // caller then uses the generic kernel. softcap c > 0 caps the scaled scores at c tanh(s / c) (with the hardware's tanh);
-// sinks (float32 [nq] or null) adds exp(sink) of the head to the softmax's denominator.
+// sinks (float32 [nq] or null) adds exp(sink) of the head to the softmax's denominator; slopes (float32 [nq] or null)
+// takes slope_h times the key's distance off every score of head h.
 extern "C" int stride_paged_prefill_attention(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                                               const int32_t* block_table, int table_width, const int32_t* q_start,
                                               const int32_t* q_len, const int32_t* ctx_len, int num_seqs, int tokens, int nq,
                                               int nkv, int hd, int page_size, float scale, int window, float softcap,
-                                              const float* sinks, cudaStream_t stream) {
+                                              const float* sinks, const float* slopes, cudaStream_t stream) {
     if (tokens < 0 || num_seqs < 0 || nq <= 0 || nkv <= 0 || page_size <= 0 || table_width <= 0 || window < 0 || softcap < 0.f)
         return STRIDE_BAD_ARGUMENT;
     if (nq % nkv) return STRIDE_BAD_ARGUMENT;
@@ -280,7 +292,7 @@ extern "C" int stride_paged_prefill_attention(const void* q, int q_stride, void*
     auto vp = static_cast<const __nv_bfloat16*>(v_pages);
     if (hd == 64)
         return launch_prefill<64>(qp, q_stride, op, kp, vp, block_table, table_width, q_start, q_len, ctx_len, num_seqs, max_tiles,
-                                  nq, nkv, page_size, scale, window, softcap, sinks, stream);
+                                  nq, nkv, page_size, scale, window, softcap, sinks, slopes, stream);
     return launch_prefill<128>(qp, q_stride, op, kp, vp, block_table, table_width, q_start, q_len, ctx_len, num_seqs, max_tiles,
-                               nq, nkv, page_size, scale, window, softcap, sinks, stream);
+                               nq, nkv, page_size, scale, window, softcap, sinks, slopes, stream);
 }

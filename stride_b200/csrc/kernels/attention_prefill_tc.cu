@@ -67,7 +67,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const int32_t* __restrict__ block_table, int table_width, const int32_t* __restrict__ q_start,
                        const int32_t* __restrict__ q_len, const int32_t* __restrict__ ctx_len, int num_seqs, int nq, int nkv,
                        int page_shift, float scale_log2e, int window, float cap_in, const float* __restrict__ sinks,
-                       int* __restrict__ status) {
+                       const float* __restrict__ slopes, int* __restrict__ status) {
     constexpr int HALVES = HD / 64;                       // 64-column boxes per row
     constexpr int HALF_BYTES = kQRows * 128;              // a [128 rows x 64 columns] bf16 box of Q
     constexpr int KV_HALF_BYTES = kKeys * 128;            // [64 keys x 64 columns] of K or V
@@ -305,6 +305,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
         const int pos_r = pos0 + min(row, rows - 1);
         float m_ref = -INFINITY, l = 0.f;                    // m_ref in log2 units (scaled scores)
+        // A penalty on the key's distance, slope (pos - key), in the units of the raw scores (which scale_log2e multiplies).
+        const float slope_raw = slopes != nullptr ? slopes[head] * 1.4426950408889634f / scale_log2e : 0.f;
         // The output product of tile x has finished when phase x / 2 of s_free[x & 1] has: the phase before it
         // (tile x - 2) is known to be over whenever this is asked, because the scores of tile x could only be issued
         // after it, so the parity cannot be mistaken.
@@ -331,6 +333,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (cap_in > 0.f) {     // capped scores: c tanh(scale s / c); scale_log2e then holds c log2(e)
 #pragma unroll
                 for (int i = 0; i < 64; ++i) sv[i] = tanh_approx(sv[i] * cap_in);
+            }
+            if (slopes != nullptr) {
+                const float d0 = static_cast<float>(k0 - pos_r);
+#pragma unroll
+                for (int i = 0; i < 64; ++i) sv[i] = fmaf(slope_raw, d0 + static_cast<float>(i), sv[i]);
             }
             if (edge) {
 #pragma unroll
@@ -449,7 +456,7 @@ template <int HD, int HEADS>
 int launch_attn(const CUtensorMap* map_q, const CUtensorMap* map_k, const CUtensorMap* map_v, const __nv_bfloat16* k_pages, const __nv_bfloat16* v_pages, __nv_bfloat16* out,
                 const int32_t* block_table, int table_width, const int32_t* q_start, const int32_t* q_len, const int32_t* ctx_len,
                 int num_seqs, int max_tiles, int nq, int nkv, int page_shift, float scale, int window, float softcap,
-                const float* sinks, int* status, cudaStream_t stream) {
+                const float* sinks, const float* slopes, int* status, cudaStream_t stream) {
     constexpr int stages = HEADS == 1 ? 2 : 4;
     constexpr int smem = (HD / 64) * (HEADS * kQRows * 128 + 2 * stages * kKeys * 128) + 1024;      // Q tiles, key ring, value ring
     static bool configured[64] = {};        // the shared-memory limit is set per kernel and device
@@ -465,11 +472,11 @@ int launch_attn(const CUtensorMap* map_q, const CUtensorMap* map_k, const CUtens
     if (map_k != nullptr && map_v != nullptr)
         stride::launch(attn_prefill_tc_kernel<HD, HEADS, true>, grid, block, smem, stream, *map_q, *map_k, *map_v, k_pages, v_pages, out,
                        block_table, table_width, q_start, q_len, ctx_len, num_seqs, nq, nkv, page_shift,
-                       (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, window, softcap > 0.f ? scale / softcap : 0.f, sinks, status);
+                       (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, window, softcap > 0.f ? scale / softcap : 0.f, sinks, slopes, status);
     else
         stride::launch(attn_prefill_tc_kernel<HD, HEADS, false>, grid, block, smem, stream, *map_q, *map_q, *map_q, k_pages, v_pages, out,
                        block_table, table_width, q_start, q_len, ctx_len, num_seqs, nq, nkv, page_shift,
-                       (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, window, softcap > 0.f ? scale / softcap : 0.f, sinks, status);
+                       (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, window, softcap > 0.f ? scale / softcap : 0.f, sinks, slopes, status);
     return STRIDE_LAUNCH_STATUS();
 }
 
@@ -501,12 +508,14 @@ static bool kv_tma() {
 // pages: [num_pages, nkv, page_size, hd]. Returns -2 for what it does not take (head sizes other
 // than 64 and 128, page sizes that are no power of two from 4 to 64, unaligned strides); the caller
 // then uses the mma.sync kernel. softcap c > 0 caps the scaled scores at c tanh(s / c) (with the hardware's tanh); sinks
-// (float32 [nq] or null) adds exp(sink) of the head to the softmax's denominator.
+// (float32 [nq] or null) adds exp(sink) of the head to the softmax's denominator; slopes (float32 [nq] or null) takes
+// slope_h times the key's distance off every score of head h.
 extern "C" int stride_paged_prefill_attention_tc(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                                                  int num_pages, const int32_t* block_table, int table_width,
                                                  const int32_t* q_start, const int32_t* q_len, const int32_t* ctx_len,
                                                  int num_seqs, int tokens, int nq, int nkv, int hd, int page_size, float scale,
-                                                 int window, float softcap, const float* sinks, int* status, cudaStream_t stream) {
+                                                 int window, float softcap, const float* sinks, const float* slopes, int* status,
+                                                 cudaStream_t stream) {
     if (tokens < 0 || num_seqs < 0 || nq <= 0 || nkv <= 0 || page_size <= 0 || table_width <= 0 || window < 0 || num_pages <= 0 ||
         softcap < 0.f)
         return STRIDE_BAD_ARGUMENT;
@@ -540,7 +549,7 @@ extern "C" int stride_paged_prefill_attention_tc(const void* q, int q_stride, vo
     }
 #define STRIDE_ATTN_LAUNCH(HD_, HEADS_)                                                                                          \
     tc::launch_attn<HD_, HEADS_>(map_q, map_k, map_v, kp, vp, op, block_table, table_width, q_start, q_len, ctx_len, num_seqs, max_tiles, nq, \
-                                 nkv, page_shift, scale, window, softcap, sinks, status, stream)
+                                 nkv, page_shift, scale, window, softcap, sinks, slopes, status, stream)
     if (hd == 64) return pair ? STRIDE_ATTN_LAUNCH(64, 2) : STRIDE_ATTN_LAUNCH(64, 1);
     return pair ? STRIDE_ATTN_LAUNCH(128, 2) : STRIDE_ATTN_LAUNCH(128, 1);
 #undef STRIDE_ATTN_LAUNCH

@@ -69,13 +69,13 @@ _SIGNATURES = {
                                                                c_int, c_float, c_int, c_int, c_void_p, c_void_p]),
     "stride_paged_decode_attention_rules": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                                                  c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
-                                                                 c_int, c_float, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p]),
+                                                                 c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "stride_paged_prefill_attention": ("attention_prefill", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                                             c_int, c_float, c_int, c_float, c_void_p, c_void_p]),
+                                                             c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p]),
     "stride_paged_prefill_attention_tc": ("attention_prefill_tc", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                                    c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                                                   c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p]),
+                                                                   c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p]),
     "stride_sample_ranked": ("sampling_ranked", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                  c_void_p, c_void_p, c_longlong, c_void_p]),
     "stride_sample_rows": ("sampling", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -1195,10 +1195,10 @@ def decode_scratch_floats(tokens: int, nq: int, nkv: int, hd: int, max_context: 
 
 def paged_attention_decode(q, q_stride: int, out, k_pages, v_pages, block_table, seq_of_token, positions, scratch, nq: int,
                            nkv: int, hd: int, page_size: int, scale: float, window: int, max_context: int, softcap: float = 0.0,
-                           sinks=None) -> None:
+                           sinks=None, slopes=None) -> None:
     """Attention for single decoded tokens (one query per row), split over the keys;
     ``scratch`` (float32, zero when first used) holds the ticket counters and the
-    partial results of the splits. ``softcap`` and ``sinks`` as for ``paged_attention``."""
+    partial results of the splits. ``softcap``, ``sinks`` and ``slopes`` as for ``paged_attention``."""
     tokens = out.shape[0]
     if out.shape[1] != nq * hd:
         raise KernelError("attention output has the wrong width")
@@ -1207,7 +1207,8 @@ def paged_attention_decode(q, q_stride: int, out, k_pages, v_pages, block_table,
         _dev(v_pages, "v_pages", torch.bfloat16), k_pages.shape[0], _dev(block_table, "block_table", torch.int32),
         block_table.shape[1], _dev(seq_of_token, "seq_of_token", torch.int32), _dev(positions, "positions", torch.int32),
         _dev(scratch, "scratch", torch.float32), scratch.numel(), tokens, nq, nkv, hd, page_size, float(scale), int(window),
-        float(softcap), _opt(sinks, "sinks", torch.float32), int(max_context), _tc_buffers(q.device, 0)["status"].data_ptr(), _stream()),
+        float(softcap), _opt(sinks, "sinks", torch.float32), _opt(slopes, "slopes", torch.float32), int(max_context),
+        _tc_buffers(q.device, 0)["status"].data_ptr(), _stream()),
         "paged_attention_decode")
 
 
@@ -1216,7 +1217,7 @@ TC_ATTENTION = _os.environ.get("STRIDE_B200_TC_ATTENTION", "1") != "0"
 
 def paged_attention_prefill_tc(q, q_stride: int, out, k_pages, v_pages, block_table, q_start, q_len, ctx_len, num_seqs: int,
                                nq: int, nkv: int, hd: int, page_size: int, scale: float, window: int, softcap: float = 0.0,
-                               sinks=None) -> bool:
+                               sinks=None, slopes=None) -> bool:
     """The tcgen05 version of ``paged_attention_prefill`` (same arguments). Returns False
     when it does not take the sizes; the caller then uses the mma.sync kernel."""
     tokens = out.shape[0]
@@ -1228,7 +1229,7 @@ def paged_attention_prefill_tc(q, q_stride: int, out, k_pages, v_pages, block_ta
         _dev(v_pages, "v_pages", torch.bfloat16), k_pages.shape[0], _dev(block_table, "block_table", torch.int32),
         block_table.shape[1], _dev(q_start, "q_start", torch.int32), _dev(q_len, "q_len", torch.int32),
         _dev(ctx_len, "ctx_len", torch.int32), num_seqs, tokens, nq, nkv, hd, page_size, float(scale), int(window), float(softcap),
-        _opt(sinks, "sinks", torch.float32), st["status"].data_ptr(), _stream())
+        _opt(sinks, "sinks", torch.float32), _opt(slopes, "slopes", torch.float32), st["status"].data_ptr(), _stream())
     if code == -2:
         return False
     _check(code, "paged_attention_prefill_tc")
@@ -1237,7 +1238,7 @@ def paged_attention_prefill_tc(q, q_stride: int, out, k_pages, v_pages, block_ta
 
 def paged_attention_prefill(q, q_stride: int, out, k_pages, v_pages, block_table, q_start, q_len, ctx_len, num_seqs: int,
                             nq: int, nkv: int, hd: int, page_size: int, scale: float, window: int, softcap: float = 0.0,
-                            sinks=None) -> None:
+                            sinks=None, slopes=None) -> None:
     """Attention for the first ``num_seqs`` requests of the step (portions of any
     length), which own the rows of ``out``. ``softcap`` and ``sinks`` as for ``paged_attention``."""
     tokens = out.shape[0]
@@ -1248,7 +1249,7 @@ def paged_attention_prefill(q, q_stride: int, out, k_pages, v_pages, block_table
         _dev(v_pages, "v_pages", torch.bfloat16), _dev(block_table, "block_table", torch.int32), block_table.shape[1],
         _dev(q_start, "q_start", torch.int32), _dev(q_len, "q_len", torch.int32), _dev(ctx_len, "ctx_len", torch.int32),
         num_seqs, tokens, nq, nkv, hd, page_size, float(scale), int(window), float(softcap), _opt(sinks, "sinks", torch.float32),
-        _stream()), "paged_attention_prefill")
+        _opt(slopes, "slopes", torch.float32), _stream()), "paged_attention_prefill")
 
 
 # --------------------------------------------------------------------- sampling

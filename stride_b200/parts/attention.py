@@ -86,11 +86,13 @@ class PagedAttention(Mixer):
             [2.0 ** (-float(slope_c) * (h + 1) / self.nq) for h in range(self.nq)], dtype=torch.float32, device=runtime.device)
         self.v_dim, self.o_in = self.nkv * self.vd, self.nq * self.vd
         self.kv_cols = 0 if self.borrows else self.kv_dim + self.v_dim
-        self.qkv_dim = self.q_dim + self.kv_cols + (self.nq if self.fused_gate else 0)
+        # gate columns are padded so that every row of the fused buffer starts on a 16-byte boundary
+        self.gate_cols = -(-self.nq // 8) * 8 if self.fused_gate else 0
+        self.qkv_dim = self.q_dim + self.kv_cols + self.gate_cols
         permutation = getattr(self.position, "head_permutation", lambda: None)()
         self.perm = None if permutation is None else torch.tensor(permutation, dtype=torch.long)
         self.w_qkv = self.w_o = self.bias = self.w_gate = self.sinks = None
-        self._fast = ops.fast_attention_supported(runtime.dtype, self.nq, self.nkv, self.hd) and self.vd == self.hd and self.slopes is None
+        self._fast = ops.fast_attention_supported(runtime.dtype, self.nq, self.nkv, self.hd) and self.vd == self.hd
         self.accepts_folded = not self.gated          # the gate reads the normed input as a tensor
 
     # ----------------------------------------------------------------- weights
@@ -162,6 +164,8 @@ class PagedAttention(Mixer):
             raise ValueError("head norms are not combined with a rotation that reorders the heads' entries")
         order = ["q"] + ([] if self.borrows else ["k", "v"])
         rows = [weights[w[n]] for n in order] + ([weights[w["g"]]] if self.fused_gate else [])
+        if self.gate_cols > self.nq:
+            rows.append(torch.zeros((self.gate_cols - self.nq, self.hidden), dtype=rows[0].dtype, device=rows[0].device))
         self.w_qkv = torch.cat(rows, dim=0).contiguous()
         self.w_o = weights[w["o"]]
         if self.spec.bias:
@@ -299,7 +303,7 @@ class PagedAttention(Mixer):
         split = min(ctx.decode_tail_start, tokens)          # portions before, single decoded tokens after
         if split > 0:
             args = (qkv[:split], self.qkv_dim, attn[:split], cache.k_pages, cache.v_pages, table, ctx.q_start, ctx.q_len,
-                    ctx.ctx_len, ctx.decode_tail_seq, *geometry, self.softcap, self.sinks)
+                    ctx.ctx_len, ctx.decode_tail_seq, *geometry, self.softcap, self.sinks, self.slopes)
             # tcgen05 kernel first; the mma.sync kernel takes what it refuses (odd page sizes)
             if not (ops.TC_ATTENTION and ops.paged_attention_prefill_tc(*args)):
                 ops.paged_attention_prefill(*args)
@@ -308,7 +312,7 @@ class PagedAttention(Mixer):
             scratch = self.rt.scratch("attention_splits", ops.decode_scratch_floats(n, self.nq, self.nkv, self.hd, ctx.context_bound))
             ops.paged_attention_decode(qkv[split:tokens], self.qkv_dim, attn[split:tokens], cache.k_pages, cache.v_pages, table,
                                        ctx.seq_of_token[split:tokens], ctx.positions[split:tokens], scratch, *geometry,
-                                       ctx.context_bound, self.softcap, self.sinks)
+                                       ctx.context_bound, self.softcap, self.sinks, self.slopes)
 
 
 register_part("mixer", "attention", PagedAttention)
