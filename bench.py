@@ -384,8 +384,7 @@ def run_profile(args) -> dict:
         from stride_b200.config import config_from_dict
         full_layers = args.layers or 6
         first = args.compare_sizes.split(",")[0]
-        cfg = config_from_dict(compare_configs_migelix(MIGELIX_SIZES[first], full_layers)[0] if args.compare == "migelix"
-                               else compare_configs(COMPARE_SIZES[first], full_layers)[0])
+        cfg = config_from_dict(_compared(args.compare, first, full_layers)[0])
         vocab, layers = cfg.vocab, full_layers
     else:
         cfg, full_layers = bench_config(args.layers, args.shape)
@@ -486,6 +485,42 @@ def compare_configs_migelix(size: dict, layers: int):
     return ours, llama
 
 
+# Layer sizes for `--compare tutizen`: attention layers with head norms, distance slopes and a gate per head; every second
+# layer borrows the pages of the layer before it and has a mixture of gated experts (with a gated shared expert) where the
+# others have the dense gated feed-forward. A token uses as many feed-forward weights in either kind of layer as in the
+# Llama decoder's (top * ff + shared = the dense inner width); the mixture holds several times as many in all.
+TUTIZEN_SIZES = {
+    "w1024": dict(width=1024, vocab=32000, ff=2752, heads=8, kv=2, dim=128, experts=16, top=2, expert_ff=896, shared_ff=960, groups=4, keep=2),
+    "w2048": dict(width=2048, vocab=32000, ff=5504, heads=16, kv=4, dim=128, experts=32, top=4, expert_ff=1024, shared_ff=1408, groups=8, keep=4),
+}
+
+
+def compare_configs_tutizen(size: dict, layers: int):
+    """(Tutizen config.json, Llama config.json) of one size."""
+    mixer = {"heads": size["heads"], "kv_heads": size["kv"], "dim": size["dim"], "vdim": size["dim"], "scale": size["dim"] ** -0.5}
+    dense = {"kind": "dense", "ff": size["ff"], "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": size["expert_ff"], "limit": 7.0}, "shared": {"ff": size["shared_ff"], "limit": 7.0},
+           "router": {"experts": size["experts"], "top": size["top"], "scale": 2.5, "groups": {"count": size["groups"], "keep": size["keep"]}}}
+    entries = [{"type": "attention", "mixer": dict(mixer, kv_from=i - 1) if i % 2 else mixer, "mlp": moe if i % 2 else dense}
+               for i in range(layers)]
+    ours = {"architecture": "Tutizen", "width": size["width"], "vocab": size["vocab"], "norm": {"eps": 1e-6}, "residual_mult": 0.7,
+            "layers": entries}
+    llama = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": layers, "hidden_size": size["width"],
+             "num_attention_heads": size["heads"], "num_key_value_heads": size["kv"], "head_dim": size["dim"],
+             "intermediate_size": size["ff"], "vocab_size": size["vocab"], "rope_theta": 500000.0, "rms_norm_eps": 1e-5,
+             "tie_word_embeddings": False, "max_position_embeddings": 8192, "hidden_act": "silu"}
+    return ours, llama
+
+
+def _compared(design: str, size_name: str, layers: int):
+    """The two configurations of ``--compare design`` at one size."""
+    if design == "migelix":
+        return compare_configs_migelix(MIGELIX_SIZES[size_name], layers)
+    if design == "tutizen":
+        return compare_configs_tutizen(TUTIZEN_SIZES[size_name], layers)
+    return compare_configs(COMPARE_SIZES[size_name], layers)
+
+
 def _measure_design(config: dict, batch: int, context: int, prompt_len: int, steps: int, warmup: int) -> dict:
     """Prefill of one prompt and a decode step of ``batch`` requests at ``context`` for one configuration: device time
     by CUDA events, and the device time per class of kernel of one eagerly run step of each."""
@@ -542,16 +577,13 @@ def _measure_design(config: dict, batch: int, context: int, prompt_len: int, ste
 
 
 def run_compare(args) -> dict:
-    """``--compare nidilix | migelix``: prefill and decode throughput of that design at a few layer sizes beside the
+    """``--compare nidilix | migelix | tutizen``: prefill and decode throughput of that design at a few layer sizes beside the
     Llama decoder at equal size, with the device time per class of kernel. Not the headline workload."""
     layers = args.layers or 6
     sizes = [s for s in args.compare_sizes.split(",") if s]
     result = {"mode": "compare", "design": args.compare, "beside": "llama", "layers": layers, "dtype": "bf16", "data": "synthetic", "sizes": {}}
     for name in sizes:
-        if args.compare == "migelix":
-            ours, llama = compare_configs_migelix(MIGELIX_SIZES[name], layers)
-        else:
-            ours, llama = compare_configs(COMPARE_SIZES[name], layers)
+        ours, llama = _compared(args.compare, name, layers)
         result["sizes"][name] = {
             args.compare: _measure_design(ours, args.batch, args.context, 2048, args.steps, args.warmup),
             "llama": _measure_design(llama, args.batch, args.context, 2048, args.steps, args.warmup)}
@@ -654,7 +686,7 @@ def main(argv=None) -> int:
     p.add_argument("--no-breakdown", action="store_true", help="skip the per-class times of one decode step and the prefill")
     p.add_argument("--profile", choices=["decode", "prefill"], default=None,
                    help="run a few eager steps of one kind for a profiler instead of measuring")
-    p.add_argument("--compare", choices=["nidilix", "migelix"], default=None,
+    p.add_argument("--compare", choices=["nidilix", "migelix", "tutizen"], default=None,
                    help="instead of the headline workload: this design's prefill and decode beside the Llama decoder at equal size")
     p.add_argument("--compare-sizes", default="w1024,w2048", help="comma-separated names of the sizes to compare")
     args = p.parse_args(argv)

@@ -436,8 +436,8 @@ def test_a_far_key_shows_through_the_heads_with_small_slopes(gpu, tmp_models, dt
 
 
 def test_the_distance_penalty_is_the_designs(gpu, tmp_models):
-    """The plain logits with the slopes of another head count (the exponent halved) differ outright from the design's, at the
-    first tokens and later; the engine gives the design's."""
+    """The plain logits with other slopes (the exponent halved) differ outright from the design's once a few keys are in
+    sight; the engine gives the design's."""
     cfg = far_model()
     state = {k: v.double() for k, v in cases.seeded_state(cfg, 43).items()}
     tokens = seeded_tokens(80, cfg["vocab"], 3)
@@ -449,7 +449,7 @@ def test_the_distance_penalty_is_the_designs(gpu, tmp_models):
     finally:
         plain.head_slopes = original
     moved = (off - full).abs().amax(dim=1) > 0.05 * full.abs().max()
-    assert moved[:8].sum() >= 3 and moved[40:].sum() >= 20
+    assert moved[10:].sum() >= 20
     folder = write_model_dir(str(tmp_models / "tutizen_slopes"), cfg, {k: v.float() for k, v in state.items()}, torch.float32)
     replay(folder, "float32", modes.whole({"s": tokens}), {"s": full}, 4, 1, "slopes whole")
     replay(folder, "float32", modes.tail_one_by_one({"s": tokens}, tail=50), {"s": full}, 4, 1, "slopes decode")
