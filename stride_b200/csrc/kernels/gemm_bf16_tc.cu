@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, OutT* __restrict__ out,
                     int ldo, int M, int N, int K, int k_blocks_per_split, float* __restrict__ partials,
                     int* __restrict__ tickets, int* __restrict__ status, const float* __restrict__ norm_partials, int norm_count,
-                    float norm_eps, int act) {
+                    float norm_eps, int act, float act_limit, float act_alpha) {
     constexpr int A_BYTES = kBlockM * kBlockK * 2;
     constexpr int B_BYTES = BLOCK_N * kBlockK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -281,10 +281,18 @@ gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         // as the unfused path: both products rounded to bfloat16, the activation in float32
                         const float g = __bfloat162float(__float2bfloat16_rn(v[j]));
                         const float u = __bfloat162float(__float2bfloat16_rn(up_rows[row][j] * fold[128 + j]));
-                        // act 0: SiLU; 1: the tanh form of GELU
-                        const float a = act == 1 ? 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)))
-                                                 : g / (1.f + __expf(-g));
-                        out[static_cast<size_t>(c) * ldo + col] = __float2bfloat16_rn(a * u);
+                        // act 0: SiLU; 1: the tanh form of GELU; 2: the clamped form g' sigmoid(alpha g') (u' + 1) with
+                        // g' = min(g, limit), u' = clamp(u, -limit, limit), evaluated as the unfused kernel does
+                        float r;
+                        if (act == 2) {
+                            const float gc = fminf(g, act_limit), uc = fminf(fmaxf(u, -act_limit), act_limit);
+                            r = gc / (1.f + expf(-act_alpha * gc)) * (uc + 1.f);
+                        } else {
+                            const float a = act == 1 ? 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)))
+                                                     : g / (1.f + __expf(-g));
+                            r = a * u;
+                        }
+                        out[static_cast<size_t>(c) * ldo + col] = __float2bfloat16_rn(r);
                     }
                 }
             }
@@ -355,7 +363,7 @@ gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 template <int BLOCK_N, int STAGES, bool TRANSPOSED, typename OutT, bool GATED = false>
 int launch(const CUtensorMap* map_a, const CUtensorMap* map_b, OutT* out, int ldo, int M, int N, int K, int splits,
            float* partials, int* tickets, int* status, cudaStream_t stream, const float* norm_partials = nullptr, int norm_count = 0,
-           float norm_eps = 0.f, int act = 0) {
+           float norm_eps = 0.f, int act = 0, float act_limit = 0.f, float act_alpha = 1.f) {
     constexpr int smem = STAGES * (kBlockM * kBlockK * 2 + BLOCK_N * kBlockK * 2) + 1024;
     static bool configured = false;
     auto kernel = gemm_tn_bf16_kernel<BLOCK_N, STAGES, TRANSPOSED, TRANSPOSED, OutT, GATED>;   // swapped use: A holds weights
@@ -368,7 +376,7 @@ int launch(const CUtensorMap* map_a, const CUtensorMap* map_b, OutT* out, int ld
     const int per_split = (k_blocks + splits - 1) / splits;
     dim3 grid((M + kBlockM - 1) / kBlockM, (N + BLOCK_N - 1) / BLOCK_N, splits);
     stride::launch(kernel, dim3(grid), dim3(kThreads), smem, stream, *map_a, *map_b, out, ldo, M, N, K, per_split, partials, tickets, status,
-                   norm_partials, norm_count, norm_eps, act);
+                   norm_partials, norm_count, norm_eps, act, act_limit, act_alpha);
     return STRIDE_LAUNCH_STATUS();
 }
 
@@ -392,7 +400,7 @@ int launch_clustered(const CUtensorMap* map_a, const CUtensorMap* map_b, OutT* o
     const int per_split = (k_blocks + splits - 1) / splits;
     dim3 grid((M + kBlockM - 1) / kBlockM, (N + BLOCK_N - 1) / BLOCK_N, splits);
     stride::launch_clusters(kernel, grid, dim3(kThreads), smem, stream, splits, *map_a, *map_b, out, ldo, M, N, K, per_split,
-                            static_cast<float*>(nullptr), static_cast<int*>(nullptr), status, static_cast<const float*>(nullptr), 0, 0.f, 0);
+                            static_cast<float*>(nullptr), static_cast<int*>(nullptr), status, static_cast<const float*>(nullptr), 0, 0.f, 0, 0.f, 1.f);
     return STRIDE_LAUNCH_STATUS();
 }
 
@@ -504,14 +512,16 @@ int stride_gemm_tc_skinny(const void* x, const void* w, void* out, int tokens, i
 #undef STRIDE_TC_LAUNCH
 }
 
-// out = act(x @ gate^T) * (x @ up^T) for at most 16 tokens (act 0: SiLU, 1: the tanh form of GELU). w: [2 * inner, k] bf16 with the rows of gate and up
+// out = act(x @ gate^T) * (x @ up^T) for at most 16 tokens (act 0: SiLU, 1: the tanh form of GELU; 2: the clamped form
+// min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u, -limit, limit) + 1) of the two products g and u). w: [2 * inner, k] bf16 with the rows of gate and up
 // alternating in blocks of 64 (gate 0-63, up 0-63, gate 64-127, ...); out: [tokens, inner] bf16. Returns -2 for
 // what it does not take (inner % 64 != 0, more than 16 tokens, sizes for which K would be split, unaligned
 // operands); the caller then runs the product and the activation separately. With norm_partials, x is the x~ of a
 // folded RMS norm (see the kernel) and the factor 1/rms per token is applied here.
 int stride_gemm_tc_gated(const void* x, const void* w, void* out, int tokens, int inner, int k, int* status,
-                         const float* norm_partials, int norm_count, float norm_eps, int act, cudaStream_t stream) {
-    if (tokens < 0 || inner <= 0 || k <= 0 || act < 0 || act > 1) return STRIDE_BAD_ARGUMENT;
+                         const float* norm_partials, int norm_count, float norm_eps, int act, float limit, float alpha,
+                         cudaStream_t stream) {
+    if (tokens < 0 || inner <= 0 || k <= 0 || act < 0 || act > 2 || (act == 2 && !(limit > 0.f))) return STRIDE_BAD_ARGUMENT;
     if (tokens == 0) return 0;
     if (status == nullptr) return STRIDE_BAD_ARGUMENT;
     if (tokens > 16 || inner % 64 || k % 8 || (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16) return STRIDE_UNSUPPORTED;
@@ -520,7 +530,7 @@ int stride_gemm_tc_gated(const void* x, const void* w, void* out, int tokens, in
     const CUtensorMap* map_b = tc::cached_map(x, tokens, k, k, 16);
     if (!map_a || !map_b) return STRIDE_UNSUPPORTED;
     return tc::launch<16, 6, true, __nv_bfloat16, true>(map_a, map_b, static_cast<__nv_bfloat16*>(out), inner, 2 * inner, tokens, k, 1,
-                                                        nullptr, nullptr, status, stream, norm_partials, norm_count, norm_eps, act);
+                                                        nullptr, nullptr, status, stream, norm_partials, norm_count, norm_eps, act, limit, alpha);
 }
 
 }  // extern "C"

@@ -37,7 +37,7 @@ _SIGNATURES = {
                                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_silu_mul": ("elementwise", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_gemm_tc_gated": ("gemm_bf16_tc", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float,
-                                              c_int, c_void_p]),
+                                              c_int, c_float, c_float, c_void_p]),
     "stride_gemm_nt_f32": ("gemm_f32", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_paged_attention_generic": ("attention_generic", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -111,6 +111,9 @@ _SIGNATURES = {
     "stride_moe_plan": ("moe", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "stride_grouped_gemm": ("moe", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                     c_float, c_int, c_void_p]),
+    "stride_grouped_gemm_tc5": ("moe_tc", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                           c_float, c_int, c_void_p, c_void_p]),
+    "stride_gather_rows": ("moe_tc", [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p]),
     "stride_moe_combine": ("moe", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_relu_squared": ("moe", [c_void_p, c_longlong, c_int, c_void_p]),
     "stride_gated_act": ("pointwise", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p]),
@@ -168,6 +171,7 @@ _CLASS_OF = {
     "stride_rglru_conv": "recurrent block: convolution",
     "stride_rglru_gates": "recurrent block: gates", "stride_rglru_scan": "recurrent block: recurrence", "stride_rglru_scan_pieces": "recurrent block: recurrence", "stride_moe_route": "router",
     "stride_moe_plan": "router", "stride_grouped_gemm": "expert products", "stride_moe_combine": "expert sum",
+    "stride_grouped_gemm_tc5": "expert products (tcgen05)", "stride_gather_rows": "expert rows gathered",
     "stride_relu_squared": "relu^2", "stride_gated_act": "act * up", "stride_pointwise": "gates and caps", "stride_weighted_sum": "sum of branches",
     "stride_delta_prepare": "delta rule: convolution, unit vectors, decay", "stride_delta_scan": "delta rule: recurrence",
     "stride_bonus_scan": "decayed memory: recurrence", "stride_shift_mix": "decayed memory: token shift",
@@ -336,7 +340,7 @@ def silu_mul(inp, out, block: int | None = None) -> None:
 
 
 ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "swish_clamped": 2}
-EPILOGUE_ACTIVATIONS = ("silu", "gelu_tanh")      # what the gate/up products can apply in their own epilogue
+EPILOGUE_ACTIVATIONS = ("silu", "gelu_tanh", "swish_clamped")      # what the tcgen05 gate/up product applies in its own epilogue
 
 
 def gated_act(inp, out, block: int | None = None, activation: str = "silu", limit: float = 0.0, alpha: float = 1.0) -> None:
@@ -735,6 +739,44 @@ def grouped_gemm(a, row_map, w, offsets, c, max_rows: int, act: int = 0, limit: 
                                       float(limit), float(alpha), kind, _stream()), "grouped_gemm")
 
 
+# Steps with at least this many (token, choice) rows run the experts' products on the tcgen05 kernel (128-row tiles
+# per expert); smaller ones, whose tiles would be mostly empty, stay on the 64-row mma.sync tiles. 0 turns it off.
+GROUPED_TC_MIN_ROWS = int(_os.environ.get("STRIDE_GROUPED_TC_MIN_ROWS", "1024"))
+
+
+def grouped_tc_wanted(dtype, rows: int) -> bool:
+    return dtype == torch.bfloat16 and GROUPED_TC_MIN_ROWS > 0 and rows >= GROUPED_TC_MIN_ROWS
+
+
+def gather_rows(x, perm, offsets, experts: int, xs, max_rows: int) -> bool:
+    """``xs[p] = x[perm[p]]`` for the rows p that the plan filled (``offsets[experts]`` of them, at most ``max_rows``). False:
+    the rows are not whole 16-byte pieces and nothing was done."""
+    if x.dtype != xs.dtype or x.shape[1] != xs.shape[1] or xs.shape[0] < max_rows:
+        raise KernelError("gather_rows wants rows of one width and element type and room for every row")
+    code = _fn("stride_gather_rows")(_dev(x, "x"), x.stride(0) * x.element_size(), _dev(perm, "perm", torch.int32),
+                                     _dev(offsets, "offsets", torch.int32), int(experts), _dev(xs, "xs"), x.shape[1] * x.element_size(),
+                                     int(max_rows), _stream())
+    if code == -2:
+        return False
+    _check(code, "gather_rows")
+    return True
+
+
+def grouped_gemm_tc(a, w, offsets, c, max_rows: int, act: int = 0, limit: float = 0.0, alpha: float = 1.0) -> bool:
+    """``grouped_gemm`` without a row map (row p of ``a`` belongs to the expert whose range holds p) on the tcgen05 kernel,
+    bfloat16 operands, ``c`` bfloat16 or float32. False when it does not take the sizes (nothing was done)."""
+    experts, n, k = w.shape
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.shape[1] != k or c.dtype not in (torch.bfloat16, torch.float32):
+        return False
+    code = _fn("stride_grouped_gemm_tc5")(_dev(a, "a"), a.stride(0), _dev(w, "w"), _dev(offsets, "offsets", torch.int32), experts, _dev(c, "c"),
+                                          c.shape[1], int(max_rows), n, k, int(act), float(limit), float(alpha),
+                                          1 if c.dtype == torch.float32 else 0, _status_ptr(a.device), _stream())
+    if code == -2:
+        return False
+    _check(code, "grouped_gemm_tc5")
+    return True
+
+
 def moe_combine(y, row_of, weights, shared, out, shared_gate=None) -> None:
     """``shared_gate``: a float32 column (one logit per token, possibly a column of a wider buffer); the shared expert's
     output is then multiplied by its sigmoid."""
@@ -1057,11 +1099,12 @@ def linear_add_norm(x, weight, residual, norm_weight, xt, partials) -> int:
     return count.value
 
 
-def linear_gated_tc(x, weight, out, folded=None, activation: str = "silu") -> bool:
+def linear_gated_tc(x, weight, out, folded=None, activation: str = "silu", limit: float = 0.0, alpha: float = 1.0) -> bool:
     """``out = act(x @ gate.T) * (x @ up.T)`` (``activation`` one of ``ACTIVATIONS``) in one tcgen05 kernel for at most 16 rows of ``x``; ``weight`` is
     [2 * inter, k] with gate and up rows alternating in blocks of ``GATED_BLOCK``. With ``folded`` (a FoldedNorm
     whose ``xt`` is ``x``) the kernel applies the norm's 1/rms itself. Returns False when the kernel does not take
-    the sizes (the caller then runs the product and ``silu_mul`` with the same block)."""
+    the sizes (the caller then runs the product and ``silu_mul`` with the same block). ``limit`` and ``alpha`` belong to
+    ``swish_clamped``."""
     m, k = x.shape
     inter = weight.shape[0] // 2
     if m > TC_GEMM_MAX_TOKENS or out.shape != (m, inter) or x.dtype != torch.bfloat16:
@@ -1070,7 +1113,7 @@ def linear_gated_tc(x, weight, out, folded=None, activation: str = "silu") -> bo
     partials, count, eps = _fold_args(folded)
     code = _fn("stride_gemm_tc_gated", f"product 2x{inter}x{k} (tcgen05, {activation} * up)")(_dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16),
                                        _dev(out, "out", torch.bfloat16), m, inter, k, st["status"].data_ptr(), partials, count, eps,
-                                       ACTIVATIONS[activation], _stream())
+                                       ACTIVATIONS[activation], float(limit), float(alpha), _stream())
     if code == -2:
         return False
     _check(code, "gemm_tc_gated")

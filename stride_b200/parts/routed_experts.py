@@ -33,6 +33,7 @@ import torch
 
 from ..csrc import ops
 from .base import FeedForward, TensorDecl, register_part
+from .swiglu import interleave_gate_up
 
 
 class RoutedExperts(FeedForward):
@@ -61,6 +62,7 @@ class RoutedExperts(FeedForward):
             raise ValueError("the clamped activation needs a positive `limit`")
         if self.shared_gate and not self.shared_ff:
             raise ValueError("a gate on the shared expert needs a shared expert")
+        self.shared_block = self.shared_ff
         self.w_router = self.bias = self.w_up = self.w_down = self.shared_up = self.shared_down = self.correction = None
 
     def _n(self, short):
@@ -104,8 +106,12 @@ class RoutedExperts(FeedForward):
         self.w_down = torch.stack([weights[self._n(f"e{e}.down")] for e in range(self.experts)]).contiguous()
         if self.shared_ff:
             self.shared_up, self.shared_down = weights[self._n("shared.up")], weights[self._n("shared.down")]
-            if self.gated:          # all gate rows, then all up rows: the layout of ``gated_act`` with one block
-                self.shared_up = torch.cat([weights[self._n("shared.gate")], self.shared_up], dim=0).contiguous()
+            if self.gated:
+                # gate and up rows alternate in blocks, as in the dense gated feed-forward: 64 rows where the tcgen05
+                # product can apply the activation in its epilogue, else all gate rows before all up rows
+                gate = weights[self._n("shared.gate")]
+                self.shared_block = ops.GATED_BLOCK if gate.dtype == torch.bfloat16 and self.shared_ff % ops.GATED_BLOCK == 0 else self.shared_ff
+                self.shared_up = interleave_gate_up(gate, self.shared_up, self.shared_block)
 
     def named_tensors(self):
         out = {self._n("router"): self.w_router[:self.experts]}
@@ -121,7 +127,9 @@ class RoutedExperts(FeedForward):
             out[self._n(f"e{e}.down")] = self.w_down[e]
         if self.shared_ff:
             if self.gated:
-                out[self._n("shared.gate")], out[self._n("shared.up")] = self.shared_up[:self.shared_ff], self.shared_up[self.shared_ff:]
+                blocks = self.shared_up.view(self.shared_ff // self.shared_block, 2, self.shared_block, self.hidden)
+                out[self._n("shared.gate")] = blocks[:, 0].reshape(self.shared_ff, self.hidden)
+                out[self._n("shared.up")] = blocks[:, 1].reshape(self.shared_ff, self.hidden)
             else:
                 out[self._n("shared.up")] = self.shared_up
             out[self._n("shared.down")] = self.shared_down
@@ -149,16 +157,20 @@ class RoutedExperts(FeedForward):
         offsets = self.rt.scratch(f"moe_offsets_{self.experts}", self.experts + 1, i32)
         ops.moe_plan(ids, self.experts, offsets, perm, row_of, rank)
         hidden_rows = self.rt.buffer("moe_hidden", tokens, top * self.ff).view(pairs, self.ff)
-        ops.grouped_gemm(x, perm, self.w_up, offsets, hidden_rows, pairs, act=2 if self.gated else 1, limit=self.limit, alpha=self.alpha)
         y = self.rt.buffer("moe_y", tokens, top * self.hidden, torch.float32).view(pairs, self.hidden)
-        ops.grouped_gemm(hidden_rows, None, self.w_down, offsets, y, pairs, act=0)
+        act = 2 if self.gated else 1
+        if not self._products_tc(x, perm, offsets, hidden_rows, y, tokens, pairs, act):
+            ops.grouped_gemm(x, perm, self.w_up, offsets, hidden_rows, pairs, act=act, limit=self.limit, alpha=self.alpha)
+            ops.grouped_gemm(hidden_rows, None, self.w_down, offsets, y, pairs, act=0)
         shared = None
         if self.shared_ff:
             mid = self.rt.buffer("moe_shared_mid", tokens, self.shared_ff)
             if self.gated:
-                both = self.rt.buffer("moe_shared_gate_up", tokens, 2 * self.shared_ff)
-                ops.linear(x, self.shared_up, both)
-                ops.gated_act(both, mid, None, "swish_clamped", self.shared_limit, self.alpha)
+                if not (self.shared_block == ops.GATED_BLOCK
+                        and ops.linear_gated_tc(x, self.shared_up, mid, None, "swish_clamped", self.shared_limit, self.alpha)):
+                    both = self.rt.buffer("moe_shared_gate_up", tokens, 2 * self.shared_ff)
+                    ops.linear(x, self.shared_up, both)
+                    ops.gated_act(both, mid, self.shared_block, "swish_clamped", self.shared_limit, self.alpha)
             else:
                 ops.linear(x, self.shared_up, mid)
                 ops.relu_squared(mid)
@@ -167,6 +179,21 @@ class RoutedExperts(FeedForward):
         out = self.rt.buffer("ffn_out", tokens, self.hidden)
         ops.moe_combine(y, row_of, weights, shared, out, logits[:, self.experts] if self.shared_gate else None)
         return out
+
+
+    def _products_tc(self, x, perm, offsets, hidden_rows, y, tokens, pairs, act) -> bool:
+        """Both products of all experts on the tcgen05 kernel, for steps of many rows: the tokens' rows are laid out
+        expert by expert first, so that every expert's rows are one block of a matrix. False: nothing was done."""
+        if not ops.grouped_tc_wanted(x.dtype, pairs):
+            return False
+        rows = self.rt.buffer("moe_rows", tokens, self.top * self.hidden).view(pairs, self.hidden)
+        if not ops.gather_rows(x, perm, offsets, self.experts, rows, pairs):
+            return False
+        if not ops.grouped_gemm_tc(rows, self.w_up, offsets, hidden_rows, pairs, act, self.limit, self.alpha):
+            return False
+        if not ops.grouped_gemm_tc(hidden_rows, self.w_down, offsets, y, pairs, 0):
+            ops.grouped_gemm(hidden_rows, None, self.w_down, offsets, y, pairs, act=0)
+        return True
 
 
 register_part("feed_forward", "routed_experts", RoutedExperts)

@@ -68,7 +68,7 @@ class SwiGLU(FeedForward):
         folded = x if isinstance(x, ops.FoldedNorm) else None
         # the tcgen05 product for a few tokens applies either activation in its epilogue, the tokens-as-rows product SiLU only
         gated = self.block == ops.GATED_BLOCK and self.activation in ops.EPILOGUE_ACTIVATIONS and (
-            ops.linear_gated_tc(folded.xt if folded else x, self.w_gate_up, act, folded, self.activation)
+            ops.linear_gated_tc(folded.xt if folded else x, self.w_gate_up, act, folded, self.activation, self.limit, self.alpha)
             or (self.activation == "silu" and ops.rows_wanted(tokens)
                 and ops.linear_rows_gated(folded.xt if folded else x, self.w_gate_up, act, folded)))
         if not gated:

@@ -188,6 +188,78 @@ def test_clamped_gate_times_up(gpu, dtype, tol, tokens, inter, block):
     close(out, gg * torch.sigmoid(1.702 * gg) * (uu + 1.0), tol)
 
 
+@pytest.mark.parametrize("tokens,inter,k,limit", [(8, 9600, 512, 7.0), (3, 960, 192, 0.8), (1, 14336, 320, 1.5)])
+def test_clamped_activation_in_the_epilogue_of_the_gate_and_up_product(gpu, tokens, inter, k, limit):
+    """The product for a few tokens that applies the clamped activation itself, against the product followed by the kernel above."""
+    from stride_b200.csrc import ops
+    from stride_b200.parts.swiglu import interleave_gate_up
+    g = torch.Generator().manual_seed(inter)
+    x = torch.randn(tokens, k, generator=g).bfloat16().cuda()
+    gate, up = ((torch.randn(inter, k, generator=g) * (2.0 / k ** 0.5)).bfloat16() for _ in range(2))      # products of spread 2: many beyond a small limit
+    w = interleave_gate_up(gate, up, ops.GATED_BLOCK).cuda()
+    out = torch.full((tokens, inter), 7.0, dtype=torch.bfloat16, device="cuda")
+    if not ops.linear_gated_tc(x, w, out, None, "swish_clamped", limit, 1.702):
+        pytest.skip("the tcgen05 product does not take these sizes")
+    both = torch.empty(tokens, 2 * inter, dtype=torch.bfloat16, device="cuda")
+    ops.linear(x, w, both)
+    unfused = torch.empty_like(out)
+    ops.gated_act(both, unfused, ops.GATED_BLOCK, "swish_clamped", limit, 1.702)
+    torch.cuda.synchronize()
+    ops.check_kernel_status()
+    close(out, unfused, 1e-2)
+    gx = (x.double().cpu() @ gate.double().T).bfloat16().double().clamp(max=limit)
+    ux = (x.double().cpu() @ up.double().T).bfloat16().double().clamp(-limit, limit)
+    close(out, gx * torch.sigmoid(1.702 * gx) * (ux + 1.0), 1e-2)
+
+
+@pytest.mark.parametrize("n,k,act,out_dtype", [(96, 72, 2, torch.bfloat16), (256, 64, 2, torch.bfloat16), (130, 200, 0, torch.float32),
+                                               (384, 136, 1, torch.bfloat16), (64, 1024, 0, torch.float32), (20, 8, 2, torch.float32)])
+def test_expert_products_on_the_tcgen05_tiles(gpu, n, k, act, out_dtype):
+    """Rows lying expert by expert, with experts of no row, one row, exactly one tile and several ragged tiles: the
+    tcgen05 grouped product against float64, and against the mma.sync tiles; rows it must not touch keep their value."""
+    from stride_b200.csrc import ops
+    g = torch.Generator().manual_seed(n * k + act)
+    counts = [0, 1, 128, 300, 0, 129, 77, 0]
+    offsets = torch.tensor([0] + torch.tensor(counts).cumsum(0).tolist(), dtype=torch.int32)
+    rows, spare = int(offsets[-1]), 40
+    a = torch.randn(rows + spare, k, generator=g).bfloat16()
+    w = (torch.randn(len(counts), n, k, generator=g) * (1.5 / k ** 0.5)).bfloat16()
+    width = n // 2 if act == 2 else n
+    out = torch.full((rows + spare, width), 3.0, dtype=out_dtype, device="cuda")
+    if not ops.grouped_gemm_tc(a.cuda(), w.cuda(), offsets.cuda(), out, rows + spare, act, 0.9, 1.702):
+        pytest.skip("the tcgen05 grouped product does not take these sizes")
+    tiles = torch.full_like(out, 3.0)
+    ops.grouped_gemm(a.cuda(), None, w.cuda(), offsets.cuda(), tiles, rows + spare, act, 0.9, 1.702)
+    torch.cuda.synchronize()
+    ops.check_kernel_status()
+    want = torch.full((rows + spare, width), 3.0, dtype=torch.float64)
+    for e, c in enumerate(counts):
+        lo = int(offsets[e])
+        z = a[lo:lo + c].double() @ w[e].double().T
+        if act == 1:
+            z = z.clamp(min=0) ** 2
+        elif act == 2:
+            gg, uu = z[:, 0::2].clamp(max=0.9), z[:, 1::2].clamp(-0.9, 0.9)
+            z = gg * torch.sigmoid(1.702 * gg) * (uu + 1.0)
+        want[lo:lo + c] = z
+    tol = 1e-2 if out_dtype == torch.bfloat16 else 2e-5
+    close(out, want, tol)
+    close(out, tiles, tol)
+    assert torch.equal(out[rows:].cpu().double(), want[rows:]), "rows past the last expert's were written"
+
+
+def test_rows_laid_out_expert_by_expert(gpu):
+    from stride_b200.csrc import ops
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(50, 72, generator=g).bfloat16()
+    perm = torch.randint(0, 50, (90,), generator=g, dtype=torch.int32)
+    offsets = torch.tensor([0, 30, 30, 81], dtype=torch.int32)          # 81 rows filled of room for 90
+    xs = torch.full((90, 72), 5.0, dtype=torch.bfloat16, device="cuda")
+    assert ops.gather_rows(x.cuda(), perm.cuda(), offsets.cuda(), 3, xs, 90)
+    torch.cuda.synchronize()
+    assert torch.equal(xs[:81].cpu(), x[perm[:81].long()]) and bool((xs[81:] == 5.0).all())
+
+
 @pytest.mark.parametrize("experts,top,groups,keep", [(12, 2, 4, 3), (8, 2, 4, 2), (6, 3, 1, 1), (4, 1, 2, 2), (9, 2, 3, 1), (64, 6, 8, 3), (256, 8, 8, 4),
                                                      (5, 5, 5, 5), (6, 2, 6, 2)])
 def test_router_with_sigmoid_scores_and_groups(gpu, experts, top, groups, keep):
@@ -231,14 +303,16 @@ def test_router_keeps_negative_choice_scores_out_of_dropped_groups(gpu):
 
 
 @pytest.mark.parametrize("dtype,tol", [("float32", 1e-5), ("bfloat16", 2e-2)])
-@pytest.mark.parametrize("width,ff,experts,top", [(96, 24, 8, 2), (100, 14, 9, 2), (128, 64, 4, 1)])
-def test_gated_experts_and_the_gated_shared_expert(gpu, tmp_models, dtype, tol, width, ff, experts, top):
-    """The routed feed-forward as a part, against the plain mixture, for inputs that drive many units into the clamp."""
+@pytest.mark.parametrize("width,ff,experts,top,tokens", [(96, 24, 8, 2, 37), (100, 14, 9, 2, 37), (128, 64, 4, 1, 37), (136, 72, 6, 3, 400),
+                                                         (64, 128, 5, 2, 700)])
+def test_gated_experts_and_the_gated_shared_expert(gpu, tmp_models, dtype, tol, width, ff, experts, top, tokens):
+    """The routed feed-forward as a part, against the plain mixture, for inputs that drive many units into the clamp; the
+    steps of many rows run the experts on the tcgen05 tiles in bfloat16."""
     from stride_b200.config import FeedForwardSpec
     from stride_b200.parts import Runtime, build_part
     cfg = cases.config(width, 50, [(cases.attn(1, 1, 8), cases.moe(experts, top, ff, 0.9, groups=None, scale=1.5, shared=(ff + 6, 0.6)))])
     state = {k: v.to(STORED[dtype]) for k, v in cases.seeded_state(cfg, 5).items() if k.startswith("l0.mlp.")}
-    rt = Runtime("cuda", STORED[dtype], 64, 4)
+    rt = Runtime("cuda", STORED[dtype], max(64, tokens), 4)
     part = build_part("feed_forward", FeedForwardSpec("routed_experts", width, ff, "swish_clamped", "l0.mlp.", params=(
         ("experts", experts), ("top", top), ("router", "sigmoid_groups"), ("route_scale", 1.5), ("limit", 0.9), ("alpha", 1.702),
         ("shared", ff + 6), ("shared_limit", 0.6), ("shared_gate", True))), rt)
@@ -247,10 +321,10 @@ def test_gated_experts_and_the_gated_shared_expert(gpu, tmp_models, dtype, tol, 
     for name, t in part.named_tensors().items():
         assert torch.equal(t.cpu().to(state[name].dtype), state[name]), name
     g = torch.Generator().manual_seed(width)
-    x = (torch.randn(37, width, generator=g) * 1.5).to(STORED[dtype])
+    x = (torch.randn(tokens, width, generator=g) * 1.5).to(STORED[dtype])
 
     class Ctx:
-        seq_of_token = torch.zeros(64, dtype=torch.int32, device="cuda")
+        seq_of_token = torch.zeros(max(64, tokens), dtype=torch.int32, device="cuda")
     out = part.forward(x.cuda(), Ctx)
     want = plain.moe_ff(x.double(), {k: v.double() for k, v in state.items()}, "l0.mlp.", cfg["layers"][0]["mlp"])
     close(out, want, tol)
