@@ -49,7 +49,7 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
                           float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ tickets,
                           __nv_bfloat16* __restrict__ out, int nq, int nkv, int page_size, float scale_log2e, int window,
                           float cap_in, const float* __restrict__ sinks, const float* __restrict__ slopes,
-                          int split_keys, int num_splits, int* __restrict__ status) {
+                          int split_keys, int num_splits, int* __restrict__ status, int gate_col) {
     pdl_trigger();
     // The step's index arrays and the keys of earlier steps are not written by the kernels before this one.
     constexpr int ROW_BYTES = HD * 2;
@@ -415,7 +415,10 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
             acc.z = fmaf(w[sp], v.z, acc.z);
             acc.w = fmaf(w[sp], v.w, acc.w);
         }
-        const float inv = 1.f / total[row];
+        float inv = 1.f / total[row];
+        // one gate per head, kept as a logit in the query's row (column gate_col + head): the output times its sigmoid
+        if (gate_col >= 0)
+            inv /= 1.f + expf(-__bfloat162float(q[static_cast<size_t>(t) * q_stride + gate_col + kvh * group + row]));
         uint2 packed;
         packed.x = pack_bf16(acc.x * inv, acc.y * inv);
         packed.y = pack_bf16(acc.z * inv, acc.w * inv);
@@ -458,7 +461,7 @@ int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, cons
                   const __nv_bfloat16* v_pages, long long cache_rows, const int32_t* block_table, int table_width,
                   const int32_t* seq_of_token, const int32_t* positions, float* part_o, float* part_ml, int* tickets, int tokens,
                   int nq, int nkv, int page_size, float scale, int window, float softcap, const float* sinks, const float* slopes,
-                  int split_keys, int num_splits, int* status, cudaStream_t stream) {
+                  int split_keys, int num_splits, int* status, int gate_col, cudaStream_t stream) {
     constexpr int smem = kStages * 4 * 2 * kTileKeys * HD * 2 + 1024;      // the rings, and room to align them to 1024 bytes
     // the merge keeps one weight per (head of the group, split) and one sum per head in the tile ring's memory
     if (static_cast<long long>(nq / nkv) * (num_splits + 1) * 4 > smem - 1024) return STRIDE_UNSUPPORTED;
@@ -487,12 +490,12 @@ int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, cons
         stride::launch(paged_decode_split_kernel<HD, true>, grid, dim3(128), smem, stream, *map_k, *map_v, q, q_stride, k_pages, v_pages,
                        block_table, table_width, seq_of_token, positions, part_o, part_ml, tickets, out, nq, nkv, page_size,
                        (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, window, softcap > 0.f ? scale / softcap : 0.f, sinks, slopes,
-                       split_keys, num_splits, status);
+                       split_keys, num_splits, status, gate_col);
     else
         stride::launch(paged_decode_split_kernel<HD, false>, grid, dim3(128), smem, stream, no_map, no_map, q, q_stride, k_pages, v_pages,
                        block_table, table_width, seq_of_token, positions, part_o, part_ml, tickets, out, nq, nkv, page_size,
                        (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, window, softcap > 0.f ? scale / softcap : 0.f, sinks, slopes,
-                       split_keys, num_splits, status);
+                       split_keys, num_splits, status, gate_col);
     return STRIDE_LAUNCH_STATUS();
 }
 
@@ -532,6 +535,14 @@ int stride_paged_decode_attention_rules(const void* q, int q_stride, void* out, 
                                         int nkv, int hd, int page_size, float scale, int window, float softcap, const float* sinks,
                                         const float* slopes, int max_context, int* status, cudaStream_t stream);
 
+// The same with one gate per head: the logits of a token's gates stand in its row of `q`, columns gate_col to gate_col + nq - 1
+// (gate_col -1: none), and head h's output is multiplied by the sigmoid of its logit in the merge of the splits.
+int stride_paged_decode_attention_gated(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
+                                        int num_pages, const int32_t* block_table, int table_width, const int32_t* seq_of_token,
+                                        const int32_t* positions, float* scratch, long long scratch_floats, int tokens, int nq,
+                                        int nkv, int hd, int page_size, float scale, int window, float softcap, const float* sinks,
+                                        const float* slopes, int gate_col, int max_context, int* status, cudaStream_t stream);
+
 // The same without the two things the TMA copies need (the number of pages and a status word): cp.async copies.
 int stride_paged_decode_attention(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                                   const int32_t* block_table, int table_width, const int32_t* seq_of_token,
@@ -560,7 +571,17 @@ int stride_paged_decode_attention_rules(const void* q, int q_stride, void* out, 
                                         const int32_t* positions, float* scratch, long long scratch_floats, int tokens, int nq,
                                         int nkv, int hd, int page_size, float scale, int window, float softcap, const float* sinks,
                                         const float* slopes, int max_context, int* status, cudaStream_t stream) {
-    if (softcap < 0.f) return STRIDE_BAD_ARGUMENT;
+    return stride_paged_decode_attention_gated(q, q_stride, out, k_pages, v_pages, num_pages, block_table, table_width, seq_of_token,
+                                               positions, scratch, scratch_floats, tokens, nq, nkv, hd, page_size, scale, window, softcap,
+                                               sinks, slopes, -1, max_context, status, stream);
+}
+
+int stride_paged_decode_attention_gated(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
+                                        int num_pages, const int32_t* block_table, int table_width, const int32_t* seq_of_token,
+                                        const int32_t* positions, float* scratch, long long scratch_floats, int tokens, int nq,
+                                        int nkv, int hd, int page_size, float scale, int window, float softcap, const float* sinks,
+                                        const float* slopes, int gate_col, int max_context, int* status, cudaStream_t stream) {
+    if (softcap < 0.f || gate_col < -1 || (gate_col >= 0 && gate_col + nq > q_stride)) return STRIDE_BAD_ARGUMENT;
     if (tokens < 0 || nq <= 0 || nkv <= 0 || page_size <= 0 || table_width <= 0 || window < 0 || max_context <= 0)
         return STRIDE_BAD_ARGUMENT;
     if (nq % nkv) return STRIDE_BAD_ARGUMENT;
@@ -582,9 +603,9 @@ int stride_paged_decode_attention_rules(const void* q, int q_stride, void* out, 
     const long long cache_rows = static_cast<long long>(num_pages) * nkv * page_size;
     if (hd == 64)
         return launch_decode<64>(qp, q_stride, op, kp, vp, cache_rows, block_table, table_width, seq_of_token, positions, part_o,
-                                 part_ml, tickets, tokens, nq, nkv, page_size, scale, window, softcap, sinks, slopes, split_keys, num_splits, status, stream);
+                                 part_ml, tickets, tokens, nq, nkv, page_size, scale, window, softcap, sinks, slopes, split_keys, num_splits, status, gate_col, stream);
     return launch_decode<128>(qp, q_stride, op, kp, vp, cache_rows, block_table, table_width, seq_of_token, positions, part_o,
-                              part_ml, tickets, tokens, nq, nkv, page_size, scale, window, softcap, sinks, slopes, split_keys, num_splits, status, stream);
+                              part_ml, tickets, tokens, nq, nkv, page_size, scale, window, softcap, sinks, slopes, split_keys, num_splits, status, gate_col, stream);
 }
 
 }  // extern "C"

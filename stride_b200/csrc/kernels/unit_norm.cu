@@ -45,6 +45,98 @@ __global__ void norm_add_kernel(float* __restrict__ residual, const T* __restric
     }
 }
 
+// Packs of 16 bytes of the compute dtype (8 bfloat16 or 4 float32) for the rows whose width is a whole number of them.
+template <typename T>
+struct Pack;
+template <>
+struct Pack<float> {
+    static constexpr int V = 4;
+    static __device__ __forceinline__ void load(const float* p, float* v) {
+        const float4 r = *reinterpret_cast<const float4*>(p);
+        v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float* v) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <>
+struct Pack<__nv_bfloat16> {
+    static constexpr int V = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
+        const uint4 r = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            v[2 * j] = f.x;
+            v[2 * j + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+        uint4 r;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+        *reinterpret_cast<uint4*>(p) = r;
+    }
+};
+
+// norm_add for rows of whole packs: the same sums in the same order per thread (a thread's elements are those of its
+// packs), 16-byte accesses. A row's result depends on the width and the block size only.
+template <typename T>
+__global__ void norm_add_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta, const float* __restrict__ bias,
+                                    const float* __restrict__ weight, T* __restrict__ copy, int hidden, float eps, float mult) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int V = Pack<T>::V;
+    extern __shared__ float row_buf[];  // hidden floats, then 32 for the reduction
+    float* scratch = row_buf + hidden;
+    const size_t t = blockIdx.x;
+    float* res = residual + t * hidden;
+    const int packs = hidden / V;
+    if (delta == nullptr) {
+        if (copy)
+            for (int p = threadIdx.x; p < packs; p += blockDim.x) {
+                float x[V];
+#pragma unroll
+                for (int j = 0; j < V; j += 4) Pack<float>::load(res + p * V + j, x + j);
+                Pack<T>::store(copy + t * hidden + p * V, x);
+            }
+        return;
+    }
+    const T* y = delta + t * hidden;
+    float sq = 0.f;
+    for (int p = threadIdx.x; p < packs; p += blockDim.x) {
+        float v[V];
+        Pack<T>::load(y + p * V, v);
+        if (bias) {
+            float b[V];
+#pragma unroll
+            for (int j = 0; j < V; j += 4) Pack<float>::load(bias + p * V + j, b + j);
+#pragma unroll
+            for (int j = 0; j < V; ++j) v[j] = __fadd_rn(v[j], b[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < V; ++j) sq = fmaf(v[j], v[j], sq);
+#pragma unroll
+        for (int j = 0; j < V; j += 4) Pack<float>::store(row_buf + p * V + j, v + j);
+    }
+    const float total = block_sum(sq, scratch);
+    const float inv = rsqrtf(total / static_cast<float>(hidden) + eps);
+    for (int p = threadIdx.x; p < packs; p += blockDim.x) {
+        float v[V], w[V], x[V];
+#pragma unroll
+        for (int j = 0; j < V; j += 4) {
+            Pack<float>::load(row_buf + p * V + j, v + j);
+            Pack<float>::load(weight + p * V + j, w + j);
+            Pack<float>::load(res + p * V + j, x + j);
+        }
+#pragma unroll
+        for (int j = 0; j < V; ++j) x[j] = __fadd_rn(x[j], __fmul_rn(mult, __fmul_rn(__fmul_rn(v[j], inv), w[j])));
+#pragma unroll
+        for (int j = 0; j < V; j += 4) Pack<float>::store(res + p * V + j, x + j);
+        if (copy) Pack<T>::store(copy + t * hidden + p * V, x);
+    }
+}
+
 constexpr int kNormWarps = 4;
 constexpr int kMaxHead = 256;
 
@@ -104,17 +196,20 @@ int stride_norm_add(float* residual, const void* delta, const float* bias, const
                     float eps, float mult, int dtype, cudaStream_t stream) {
     if (tokens < 0 || hidden <= 0 || (delta != nullptr && weight == nullptr)) return STRIDE_BAD_ARGUMENT;
     if (tokens == 0) return 0;
-    const int threads = hidden >= 2048 ? 512 : hidden >= 512 ? 256 : 128;
+    const int threads = hidden >= 4096 ? 512 : hidden >= 1024 ? 256 : 128;
     const size_t smem = (static_cast<size_t>(hidden) + 32) * sizeof(float);
     if (smem > 200 * 1024) return STRIDE_UNSUPPORTED;
+    auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    const bool vec = hidden % 8 == 0 && aligned(residual) && aligned(delta) && aligned(bias) && aligned(weight) && aligned(copy);
     if (dtype == STRIDE_DTYPE_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(norm_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        stride::launch(norm_add_kernel<float>, dim3(tokens), dim3(threads), smem, stream, residual, static_cast<const float*>(delta), bias,
+        auto kernel = vec ? norm_add_vec_kernel<float> : norm_add_kernel<float>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        stride::launch(kernel, dim3(tokens), dim3(threads), smem, stream, residual, static_cast<const float*>(delta), bias,
                        weight, static_cast<float*>(copy), hidden, eps, mult);
     } else if (dtype == STRIDE_DTYPE_BF16) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(norm_add_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        stride::launch(norm_add_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), smem, stream, residual,
+        auto kernel = vec ? norm_add_vec_kernel<__nv_bfloat16> : norm_add_kernel<__nv_bfloat16>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        stride::launch(kernel, dim3(tokens), dim3(threads), smem, stream, residual,
                        static_cast<const __nv_bfloat16*>(delta), bias, weight, static_cast<__nv_bfloat16*>(copy), hidden, eps, mult);
     } else {
         return STRIDE_BAD_ARGUMENT;

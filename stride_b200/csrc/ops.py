@@ -70,6 +70,9 @@ _SIGNATURES = {
     "stride_paged_decode_attention_rules": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                                                  c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
                                                                  c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "stride_paged_decode_attention_gated": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                                                 c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
+                                                                 c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "stride_paged_prefill_attention": ("attention_prefill", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                                              c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p]),
@@ -160,7 +163,7 @@ _CLASS_OF = {
     "stride_embed_gather": "embedding", "stride_add_rmsnorm": "norm", "stride_add_residual": "residual sum",
     "stride_scale_rows": "norm", "stride_zero_fresh_state": "state slots", "stride_rope_kv_write": "rotation + cache write",
     "stride_silu_mul": "silu * up", "stride_paged_attention_generic": "attention (exact kernel)",
-    "stride_paged_decode_attention_tma": "attention (decode)", "stride_paged_decode_attention_rules": "attention (decode)", "stride_paged_prefill_attention": "attention (prefill, mma.sync)",
+    "stride_paged_decode_attention_tma": "attention (decode)", "stride_paged_decode_attention_rules": "attention (decode)", "stride_paged_decode_attention_gated": "attention (decode)", "stride_paged_prefill_attention": "attention (prefill, mma.sync)",
     "stride_paged_prefill_attention_tc": "attention (prefill, tcgen05)", "stride_sample_rows": "sampling", "stride_sample_ranked": "sampling",
     "stride_add_dyt": "norm", "stride_add_scaled": "residual sum", "stride_token_side": "token side input",
     "stride_latent_prepare": "latent norm + rotation + cache write", "stride_head_gemm": "per-head product",
@@ -1238,19 +1241,21 @@ def decode_scratch_floats(tokens: int, nq: int, nkv: int, hd: int, max_context: 
 
 def paged_attention_decode(q, q_stride: int, out, k_pages, v_pages, block_table, seq_of_token, positions, scratch, nq: int,
                            nkv: int, hd: int, page_size: int, scale: float, window: int, max_context: int, softcap: float = 0.0,
-                           sinks=None, slopes=None) -> None:
+                           sinks=None, slopes=None, gate_col: int = -1) -> None:
     """Attention for single decoded tokens (one query per row), split over the keys;
     ``scratch`` (float32, zero when first used) holds the ticket counters and the
-    partial results of the splits. ``softcap``, ``sinks`` and ``slopes`` as for ``paged_attention``."""
+    partial results of the splits. ``softcap``, ``sinks`` and ``slopes`` as for ``paged_attention``. ``gate_col`` >= 0: columns
+    ``gate_col .. gate_col + nq - 1`` of a row of ``q`` hold one logit per head, and head h's output leaves the kernel
+    multiplied by the sigmoid of its logit."""
     tokens = out.shape[0]
     if out.shape[1] != nq * hd:
         raise KernelError("attention output has the wrong width")
-    _check(_fn("stride_paged_decode_attention_rules")(
+    _check(_fn("stride_paged_decode_attention_gated")(
         _dev(q, "q", torch.bfloat16), q_stride, _dev(out, "out", torch.bfloat16), _dev(k_pages, "k_pages", torch.bfloat16),
         _dev(v_pages, "v_pages", torch.bfloat16), k_pages.shape[0], _dev(block_table, "block_table", torch.int32),
         block_table.shape[1], _dev(seq_of_token, "seq_of_token", torch.int32), _dev(positions, "positions", torch.int32),
         _dev(scratch, "scratch", torch.float32), scratch.numel(), tokens, nq, nkv, hd, page_size, float(scale), int(window),
-        float(softcap), _opt(sinks, "sinks", torch.float32), _opt(slopes, "slopes", torch.float32), int(max_context),
+        float(softcap), _opt(sinks, "sinks", torch.float32), _opt(slopes, "slopes", torch.float32), int(gate_col), int(max_context),
         _tc_buffers(q.device, 0)["status"].data_ptr(), _stream()),
         "paged_attention_decode")
 

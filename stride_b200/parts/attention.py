@@ -243,9 +243,10 @@ class PagedAttention(Mixer):
             ops.linear(x, self.w_qkv, qkv)
             self.position.encode_and_store(qkv, self.bias, ctx, cache, self.nq, self.nkv, self.hd)
         attn = self.rt.buffer("attn", tokens, self.o_in)
-        self._attend(qkv, attn, ctx, cache, tokens)
+        ungated = self._attend(qkv, attn, ctx, cache, tokens)
         if self.fused_gate:
-            ops.head_gate(attn, qkv[:, self.q_dim + self.kv_cols:], self.qkv_dim, self.nq, self.vd)
+            if ungated:         # the decode kernel applies the gates of its rows itself
+                ops.head_gate(attn[:ungated], qkv[:ungated, self.q_dim + self.kv_cols:], self.qkv_dim, self.nq, self.vd)
         elif self.head_gate:
             gate = self.rt.buffer("attn_gate", tokens, self.nq)
             ops.linear(x, self.w_gate, gate)
@@ -292,14 +293,16 @@ class PagedAttention(Mixer):
         return ops.linear_qkv_rope(x, self.w_qkv, qkv, self.bias, ctx.positions[:tokens], slots, cos, sin, cache.k_pages,
                                    cache.v_pages, self.nq, self.nkv, self.hd, cache.page_size, rotate, folded)
 
-    def _attend(self, qkv, attn, ctx, cache, tokens):
+    def _attend(self, qkv, attn, ctx, cache, tokens) -> int:
+        """Attention of the step's rows. Returns how many leading rows still lack the per-head gate (all of them unless the
+        gates' logits stand in the rows of ``qkv`` and the decode kernel took the rows after the portions)."""
         table = ctx.block_table[cache.group]
         geometry = (self.nq, self.nkv, self.hd, cache.page_size, self.scale, self.window)
         if not self._fast:
             # the exact kernel: the whole 32-bit path, and bfloat16 sizes the tensor-core kernels refuse
             ops.paged_attention(qkv, self.qkv_dim, attn, cache.k_pages, cache.v_pages, table, ctx.seq_of_token[:tokens],
                                 ctx.positions[:tokens], *geometry, self.softcap, self.sinks, self.slopes, self.vd)
-            return
+            return tokens
         split = min(ctx.decode_tail_start, tokens)          # portions before, single decoded tokens after
         if split > 0:
             args = (qkv[:split], self.qkv_dim, attn[:split], cache.k_pages, cache.v_pages, table, ctx.q_start, ctx.q_len,
@@ -312,7 +315,10 @@ class PagedAttention(Mixer):
             scratch = self.rt.scratch("attention_splits", ops.decode_scratch_floats(n, self.nq, self.nkv, self.hd, ctx.context_bound))
             ops.paged_attention_decode(qkv[split:tokens], self.qkv_dim, attn[split:tokens], cache.k_pages, cache.v_pages, table,
                                        ctx.seq_of_token[split:tokens], ctx.positions[split:tokens], scratch, *geometry,
-                                       ctx.context_bound, self.softcap, self.sinks, self.slopes)
+                                       ctx.context_bound, self.softcap, self.sinks, self.slopes,
+                                       self.q_dim + self.kv_cols if self.fused_gate else -1)
+            return split if self.fused_gate else tokens
+        return tokens
 
 
 register_part("mixer", "attention", PagedAttention)

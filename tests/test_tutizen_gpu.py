@@ -84,7 +84,7 @@ def model_case(tmp_models, name, cfg, dtype, seed, lengths):
 
 # ------------------------------------------------------------------------------------------- small kernels
 @pytest.mark.parametrize("dtype,tol", [("float32", 3e-6), ("bfloat16", 1e-2)])
-@pytest.mark.parametrize("width,with_bias", [(54, True), (64, False), (320, True)])
+@pytest.mark.parametrize("width,with_bias", [(54, True), (64, False), (320, True), (2048, True), (1032, False)])
 def test_norm_on_a_sublayers_output(gpu, dtype, tol, width, with_bias):
     """x + m g unit_rms(y + b) through the part, with the copy that the next sublayer reads."""
     from stride_b200.config import NormSpec
@@ -166,13 +166,16 @@ def test_head_norms_and_the_cache_write(gpu, dtype, tol, nq, nkv, hd, vd, extra)
 
 
 def test_one_gate_per_head(gpu):
+    """Head widths that are whole 16-byte packs (the vector kernel) and one that is not; the gates stand in a column block of a wider buffer."""
     from stride_b200.csrc import ops
     g = torch.Generator().manual_seed(2)
     for dtype, tol in ((torch.float32, 3e-6), (torch.bfloat16, 1e-2)):
-        x, wide = torch.randn(5, 3 * 10, generator=g).to(dtype), (torch.randn(5, 17, generator=g) * 3).to(dtype)
-        a, w = x.cuda(), wide.cuda()
-        ops.head_gate(a, w[:, 9:], 17, 3, 10)
-        close(a, (x.double().view(5, 3, 10) * torch.sigmoid(wide.double()[:, 9:12])[:, :, None]).reshape(5, 30), tol)
+        for tokens, heads, width in ((5, 3, 10), (7, 3, 16), (300, 5, 64), (2, 1, 8)):
+            x, wide = torch.randn(tokens, heads * width, generator=g).to(dtype), (torch.randn(tokens, 17, generator=g) * 3).to(dtype)
+            a, w = x.cuda(), wide.cuda()
+            ops.head_gate(a, w[:, 9:], 17, heads, width)
+            want = x.double().view(tokens, heads, width) * torch.sigmoid(wide.double()[:, 9:9 + heads])[:, :, None]
+            close(a, want.reshape(tokens, heads * width), tol)
 
 
 @pytest.mark.parametrize("dtype,tol", [("float32", 3e-6), ("bfloat16", 1e-2)])
@@ -388,7 +391,7 @@ def test_tensor_core_attention_with_slopes_against_the_exact_kernel(gpu, nq, nkv
     g = torch.Generator().manual_seed(nq * hd)
     lens = [(0, 150), (40, 9), (130, 1), (257, 1)]               # single tokens last, as the step function lays a batch out
     k, v, table, q_start, q_len, ctx_len, seq_of, positions, tokens = paged_case(g, lens, page, nkv, hd, hd)
-    stride = nq * hd + 8
+    stride = nq * hd + 16                                        # sixteen more columns: one gate per head stands there
     q = (torch.randn(tokens, stride, generator=g) * 0.6).bfloat16().cuda()
     slopes, scale = slopes_of(nq).cuda(), 0.2
     want = torch.zeros(tokens, nq * hd, dtype=torch.bfloat16, device="cuda")
@@ -408,6 +411,15 @@ def test_tensor_core_attention_with_slopes_against_the_exact_kernel(gpu, nq, nkv
         torch.cuda.synchronize()
         ops.check_kernel_status()
         close(got, want, 2e-2)
+    # the decode kernel with one gate per head, its logits in the query's row
+    gated = torch.full((tokens - split, nq * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    scratch = torch.zeros(ops.decode_scratch_floats(2, nq, nkv, hd, 512), device="cuda")
+    ops.paged_attention_decode(q[split:], stride, gated, k, v, table, seq_of[split:], positions[split:], scratch, nq, nkv, hd, page,
+                               scale, window, 512, softcap, None, slopes, nq * hd)
+    torch.cuda.synchronize()
+    ops.check_kernel_status()
+    gates = torch.sigmoid(q[split:, nq * hd:nq * hd + nq].double())
+    close(gated, (want[split:].double().view(-1, nq, hd) * gates[:, :, None]).reshape(-1, nq * hd), 2e-2)
 
 
 # ------------------------------------------------------------------- each mechanism in a model of nothing else
