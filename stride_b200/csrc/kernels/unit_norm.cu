@@ -103,6 +103,40 @@ __global__ void norm_add_vec_kernel(float* __restrict__ residual, const T* __res
         return;
     }
     const T* y = delta + t * hidden;
+    if (packs <= static_cast<int>(blockDim.x)) {
+        // A pack a thread: everything the row needs is asked for before the sum, and nothing passes through shared
+        // memory. The sums are those of the loops below (a thread's sum is its pack's).
+        const int p = threadIdx.x;
+        const bool on = p < packs;
+        float v[V], w[V], x[V];
+        float sq1 = 0.f;
+        if (on) {
+            Pack<T>::load(y + p * V, v);
+#pragma unroll
+            for (int j = 0; j < V; j += 4) {
+                Pack<float>::load(weight + p * V + j, w + j);
+                Pack<float>::load(res + p * V + j, x + j);
+            }
+            if (bias) {
+                float b[V];
+#pragma unroll
+                for (int j = 0; j < V; j += 4) Pack<float>::load(bias + p * V + j, b + j);
+#pragma unroll
+                for (int j = 0; j < V; ++j) v[j] = __fadd_rn(v[j], b[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < V; ++j) sq1 = fmaf(v[j], v[j], sq1);
+        }
+        const float inv1 = rsqrtf(block_sum(sq1, scratch) / static_cast<float>(hidden) + eps);
+        if (on) {
+#pragma unroll
+            for (int j = 0; j < V; ++j) x[j] = __fadd_rn(x[j], __fmul_rn(mult, __fmul_rn(__fmul_rn(v[j], inv1), w[j])));
+#pragma unroll
+            for (int j = 0; j < V; j += 4) Pack<float>::store(res + p * V + j, x + j);
+            if (copy) Pack<T>::store(copy + t * hidden + p * V, x);
+        }
+        return;
+    }
     float sq = 0.f;
     for (int p = threadIdx.x; p < packs; p += blockDim.x) {
         float v[V];
@@ -186,6 +220,69 @@ qkv_unit_norm_kernel(T* __restrict__ qkv, int row_stride, const float* __restric
     }
 }
 
+// qkv_unit_norm for heads of whole packs on 16-byte boundaries: a lane holds whole packs of its head (pack p of the head
+// for p = lane, lane + 32, ...), so a warp moves a head in one or two 16-byte accesses a lane. The order of a head's sum
+// depends on its width and on LANES only. LANES = 16: two heads a warp, for heads of at most 16 packs (the sum then stays
+// inside a half warp).
+template <typename T, int LANES>
+__global__ void __launch_bounds__(kNormWarps * 32)
+qkv_unit_norm_vec_kernel(T* __restrict__ qkv, int row_stride, const float* __restrict__ bias, const int32_t* __restrict__ slot_mapping,
+                         T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv, int hd, int vd, int page_size, float eps,
+                         int norm_qk, int norm_v) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int V = Pack<T>::V;
+    constexpr int kPacks = LANES == 32 ? kMaxHead / (32 * V) : 1;
+    constexpr int kPerWarp = 32 / LANES;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & (LANES - 1);
+    const int t = blockIdx.x;
+    // query heads, then key heads, then value heads
+    const int head = (blockIdx.y * kNormWarps + warp) * kPerWarp + ((threadIdx.x & 31) / LANES);
+    const bool live = head < nq + 2 * nkv;        // a half warp without a head still takes part in the shuffles
+    const bool is_value = head >= nq + nkv;
+    const int width = live ? (is_value ? vd : hd) : 0;
+    const int column = is_value ? (nq + nkv) * hd + (head - nq - nkv) * vd : head * hd;
+    T* x = qkv + static_cast<size_t>(t) * row_stride + (live ? column : 0);
+    float v[kPacks][V];
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < kPacks; ++i) {
+        const int d = (lane + LANES * i) * V;
+        if (d < width) {
+            Pack<T>::load(x + d, v[i]);
+            if (bias) {
+                float b[V];
+#pragma unroll
+                for (int j = 0; j < V; j += 4) Pack<float>::load(bias + column + d + j, b + j);
+#pragma unroll
+                for (int j = 0; j < V; ++j) v[i][j] = __fadd_rn(v[i][j], b[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < V; ++j) sq = fmaf(v[i][j], v[i][j], sq);
+        }
+    }
+    const bool normed = is_value ? norm_v != 0 : norm_qk != 0;
+#pragma unroll
+    for (int o = LANES / 2; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    const float inv = normed && live ? rsqrtf(sq / static_cast<float>(width) + eps) : 1.f;
+    const int slot = (slot_mapping && live && head >= nq) ? slot_mapping[t] : -1;
+    T* dst = nullptr;
+    if (slot >= 0) {
+        const int kvh = is_value ? head - nq - nkv : head - nq;
+        dst = (is_value ? v_pages : k_pages) + ((static_cast<size_t>(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * width;
+    }
+#pragma unroll
+    for (int i = 0; i < kPacks; ++i) {
+        const int d = (lane + LANES * i) * V;
+        if (d < width) {
+#pragma unroll
+            for (int j = 0; j < V; ++j) v[i][j] = __fmul_rn(v[i][j], inv);
+            Pack<T>::store(x + d, v[i]);
+            if (dst) Pack<T>::store(dst + d, v[i]);
+        }
+    }
+}
+
 }  // namespace stride
 
 using namespace stride;
@@ -226,14 +323,23 @@ int stride_qkv_unit_norm(void* qkv, int row_stride, const float* bias, const int
     if (hd > kMaxHead || vd > kMaxHead) return STRIDE_UNSUPPORTED;
     if (tokens == 0 || nq + nkv == 0) return 0;
     const dim3 grid(tokens, (nq + 2 * nkv + kNormWarps - 1) / kNormWarps);
+    auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    const int pack = dtype == STRIDE_DTYPE_F32 ? 4 : 8;
+    const bool vec = hd % pack == 0 && vd % pack == 0 && row_stride % pack == 0 && aligned(qkv) && aligned(bias) && aligned(k_pages) &&
+                     aligned(v_pages);
+    const bool halves = vec && hd <= 16 * pack && vd <= 16 * pack;       // two heads a warp
+    const dim3 grid_h(tokens, ((nq + 2 * nkv + 1) / 2 + kNormWarps - 1) / kNormWarps);
     if (dtype == STRIDE_DTYPE_F32)
-        stride::launch(qkv_unit_norm_kernel<float>, grid, dim3(kNormWarps * 32), 0, stream, static_cast<float*>(qkv), row_stride, bias,
-                       slot_mapping, static_cast<float*>(k_pages), static_cast<float*>(v_pages), nq, nkv, hd, vd, page_size, eps, norm_qk,
-                       norm_v);
+        stride::launch(halves ? qkv_unit_norm_vec_kernel<float, 16> : vec ? qkv_unit_norm_vec_kernel<float, 32> : qkv_unit_norm_kernel<float>,
+                       halves ? grid_h : grid, dim3(kNormWarps * 32), 0, stream, static_cast<float*>(qkv), row_stride, bias, slot_mapping,
+                       static_cast<float*>(k_pages), static_cast<float*>(v_pages), nq, nkv, hd, vd, page_size, eps, norm_qk, norm_v);
     else if (dtype == STRIDE_DTYPE_BF16)
-        stride::launch(qkv_unit_norm_kernel<__nv_bfloat16>, grid, dim3(kNormWarps * 32), 0, stream, static_cast<__nv_bfloat16*>(qkv),
-                       row_stride, bias, slot_mapping, static_cast<__nv_bfloat16*>(k_pages), static_cast<__nv_bfloat16*>(v_pages), nq, nkv,
-                       hd, vd, page_size, eps, norm_qk, norm_v);
+        stride::launch(halves ? qkv_unit_norm_vec_kernel<__nv_bfloat16, 16>
+                       : vec  ? qkv_unit_norm_vec_kernel<__nv_bfloat16, 32>
+                              : qkv_unit_norm_kernel<__nv_bfloat16>,
+                       halves ? grid_h : grid, dim3(kNormWarps * 32), 0, stream, static_cast<__nv_bfloat16*>(qkv), row_stride, bias,
+                       slot_mapping, static_cast<__nv_bfloat16*>(k_pages), static_cast<__nv_bfloat16*>(v_pages), nq, nkv, hd, vd, page_size,
+                       eps, norm_qk, norm_v);
     else
         return STRIDE_BAD_ARGUMENT;
     return STRIDE_LAUNCH_STATUS();

@@ -84,7 +84,7 @@ def model_case(tmp_models, name, cfg, dtype, seed, lengths):
 
 # ------------------------------------------------------------------------------------------- small kernels
 @pytest.mark.parametrize("dtype,tol", [("float32", 3e-6), ("bfloat16", 1e-2)])
-@pytest.mark.parametrize("width,with_bias", [(54, True), (64, False), (320, True), (2048, True), (1032, False)])
+@pytest.mark.parametrize("width,with_bias", [(54, True), (64, False), (320, True), (2048, True), (1032, False), (4104, True)])
 def test_norm_on_a_sublayers_output(gpu, dtype, tol, width, with_bias):
     """x + m g unit_rms(y + b) through the part, with the copy that the next sublayer reads."""
     from stride_b200.config import NormSpec
