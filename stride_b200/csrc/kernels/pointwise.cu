@@ -188,7 +188,8 @@ __global__ void add_sinusoid_kernel(float* __restrict__ x, T* __restrict__ copy,
     const size_t t = blockIdx.x;
     const bool live = seq_of_token == nullptr || seq_of_token[t] >= 0;
     const double p = static_cast<double>(positions[t]);
-    for (int i = threadIdx.x; 2 * i < width; i += blockDim.x) {
+    // a pair a thread, the pairs of a row spread over blockIdx.y: the float64 sine and cosine are the kernel's time
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; 2 * i < width; i += gridDim.y * blockDim.x) {
         double s = 0.0, c = 0.0;
         if (live) sincos(p * freq[i], &s, &c);
         const size_t at = t * width + 2 * i;
@@ -298,11 +299,13 @@ int stride_add_sinusoid(float* x, void* copy, const int32_t* positions, const in
                         int width, int dtype, cudaStream_t stream) {
     if (tokens < 0 || width <= 0) return STRIDE_BAD_ARGUMENT;
     if (tokens == 0) return 0;
+    const int slices = ((width + 1) / 2 + 127) / 128;
+    const dim3 grid(tokens, slices < 65535 ? slices : 65535);
     if (dtype == STRIDE_DTYPE_F32)
-        stride::launch(add_sinusoid_kernel<float>, dim3(tokens), dim3(128), 0, stream, x, static_cast<float*>(copy), positions, seq_of_token,
+        stride::launch(add_sinusoid_kernel<float>, grid, dim3(128), 0, stream, x, static_cast<float*>(copy), positions, seq_of_token,
                        freq, width);
     else if (dtype == STRIDE_DTYPE_BF16)
-        stride::launch(add_sinusoid_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), 0, stream, x, static_cast<__nv_bfloat16*>(copy), positions,
+        stride::launch(add_sinusoid_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, x, static_cast<__nv_bfloat16*>(copy), positions,
                        seq_of_token, freq, width);
     else
         return STRIDE_BAD_ARGUMENT;
