@@ -101,7 +101,8 @@ class StreamInputSpec:
 class LayerSpec:
     """kind ``pre_norm``: x += m * mixer(norm(x)); x += m * ffn(norm(x)); then every part of ``after`` adds
     m * part(x, tokens). ``residual_mult`` is m (1 where an architecture has none); ``feed_forward`` and
-    ``ffn_norm`` may be None for a layer without a feed-forward."""
+    ``ffn_norm`` may be None for a layer without a feed-forward. kind ``sandwich`` has a second norm on either
+    sublayer's output (``mixer_out_norm``, ``ffn_out_norm``): x += m * out_norm(mixer(norm(x)))."""
     kind: str
     mixer: MixerSpec
     feed_forward: Optional[FeedForwardSpec]
@@ -109,16 +110,33 @@ class LayerSpec:
     ffn_norm: Optional[NormSpec]
     residual_mult: float = 1.0
     after: tuple = ()           # of StreamInputSpec
+    mixer_out_norm: Optional[NormSpec] = None
+    ffn_out_norm: Optional[NormSpec] = None
 
 
 @dataclass(frozen=True)
 class ScheduleEntry:
     """One run of a layer. ``cache`` names the cache slot (and state slot) that the
     run's mixer uses; two runs with the same slot share keys and values, and
-    ``writes_cache=False`` makes a run read what another run wrote."""
+    ``writes_cache=False`` makes a run read what another run wrote. ``enters_pass`` t: the run is the first of pass t
+    over a block of layers that runs several times, and the model's ``pass_input`` part works on the stream before it."""
     layer: int
     cache: int
     writes_cache: bool = True
+    enters_pass: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class PassInputSpec:
+    """What happens to the residual stream before every pass over a repeated block of layers. kind ``mix_embedding``:
+    ``x <- W [x; x0] + s[t]`` with x0 the embedding's output, ``W`` the tensor ``mix_name`` [hidden, 2 * hidden] (the
+    stream's columns first) and ``s`` the tensor ``step_name`` [passes, hidden], t the number of the pass."""
+    kind: str
+    hidden: int
+    passes: int
+    mix_name: str
+    step_name: str
+    params: tuple = ()
 
 
 @dataclass(frozen=True)
@@ -162,6 +180,7 @@ class ModelSpec:
     # names above: a table lookup and a linear head.
     embedding: Optional[EmbeddingSpec] = None
     head: Optional[HeadSpec] = None
+    pass_input: Optional[PassInputSpec] = None      # for schedules whose entries name ``enters_pass``
 
     def embedding_spec(self) -> EmbeddingSpec:
         return self.embedding or EmbeddingSpec("lookup", self.vocab, self.hidden, self.embed_name)

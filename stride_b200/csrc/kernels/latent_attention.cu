@@ -21,12 +21,13 @@
 namespace stride {
 
 // ------------------------------------------------------------------------------------------------ prepare
-// proj: [tokens, ld]; queries at column q_off, head a at q_off + a * (dim + rot), plain part first; the latent
-// projection (rank + rot columns) at kv_off, or kv_off < 0 for a layer that reads another layer's cache.
+// q: [tokens, ldq], head a at column a * (dim + rot), plain part first (a column block of proj, or a buffer of its own
+// when the queries come through a latent); proj: [tokens, ld] with the latent projection (rank + rot columns) at
+// kv_off, or kv_off < 0 for a layer that reads another layer's cache.
 // qa: [tokens, heads, rank + rot]; this kernel fills the last rot columns of every head.
 template <typename T>
 __global__ void __launch_bounds__(128)
-latent_prepare_kernel(const T* __restrict__ proj, int ld, int q_off, int kv_off, T* __restrict__ qa,
+latent_prepare_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ proj, int ld, int kv_off, T* __restrict__ qa,
                       const int32_t* __restrict__ positions, const int32_t* __restrict__ seq_of_token,
                       const int32_t* __restrict__ slot_mapping, const float* __restrict__ cos_table,
                       const float* __restrict__ sin_table, const float* __restrict__ latent_w, float eps,
@@ -44,7 +45,7 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, int q_off, int kv_off,
     T* qrow = qa + static_cast<size_t>(t) * heads * (rank + rot);
     for (int i = threadIdx.x; i < heads * rot; i += blockDim.x) {
         const int a = i / rot, j = i % rot;
-        const T* src = row + q_off + a * (dim + rot) + dim;
+        const T* src = q + static_cast<size_t>(t) * ldq + a * (dim + rot) + dim;
         float v = to_f32(src[j]);
         if (j < rot_dims) {
             const int pair = j >> 1;
@@ -79,13 +80,14 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, int q_off, int kv_off,
 }
 
 // ---------------------------------------------------------------------------------------------- head_gemm
-// C[t, a, n] = (sum_k A[t * lda + a * a_hs + k] * B[a * b_hs + k * b_ks + n * b_ns]) * (gate ? sigmoid(gate[t * ldg + a]) : 1)
+// C[t, a, n] = (sum_k A[t * lda + a * a_hs + k] * B[a * b_hs + k * b_ks + n * b_ns]) * (gate ? sigmoid(gate[t * ldg + a * g_hs + n * g_ns]) : 1)
+// (g_hs 1 and g_ns 0: one gate a head; g_hs N and g_ns 1: one gate an output)
 constexpr int HM = 32, HN = 64, HK = 16;
 
 template <typename T>
 __global__ void __launch_bounds__(256)
 head_gemm_kernel(const T* __restrict__ A, int lda, int a_hs, const T* __restrict__ B, long long b_hs, int b_ks, int b_ns,
-                 T* __restrict__ C, int ldc, int c_hs, const T* __restrict__ gate, int ldg, int M, int N, int K) {
+                 T* __restrict__ C, int ldc, int c_hs, const T* __restrict__ gate, int ldg, int g_hs, int g_ns, int M, int N, int K) {
     pdl_trigger();
     pdl_wait();
     __shared__ float As[HK][HM + 1];
@@ -125,11 +127,13 @@ head_gemm_kernel(const T* __restrict__ A, int lda, int a_hs, const T* __restrict
         const int m = m0 + ty * 2 + i;
         if (m >= M) continue;
         float g = 1.f;
-        if (gate) g = 1.f / (1.f + expf(-to_f32(gate[static_cast<size_t>(m) * ldg + a])));
+        if (gate && !g_ns) g = 1.f / (1.f + expf(-to_f32(gate[static_cast<size_t>(m) * ldg + static_cast<size_t>(a) * g_hs])));
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
-            if (n < N) C[static_cast<size_t>(m) * ldc + static_cast<size_t>(a) * c_hs + n] = from_f32<T>(acc[i][j] * g);
+            if (n >= N) continue;
+            if (gate && g_ns) g = 1.f / (1.f + expf(-to_f32(gate[static_cast<size_t>(m) * ldg + static_cast<size_t>(a) * g_hs + static_cast<size_t>(n) * g_ns])));
+            C[static_cast<size_t>(m) * ldc + static_cast<size_t>(a) * c_hs + n] = from_f32<T>(acc[i][j] * g);
         }
     }
 }
@@ -137,8 +141,8 @@ head_gemm_kernel(const T* __restrict__ A, int lda, int a_hs, const T* __restrict
 // The same on the tensor cores for bfloat16 (mma_tile.cuh): 64 tokens x 64 columns of one head a CTA.
 __global__ void __launch_bounds__(128)
 head_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, int lda, int a_hs, const __nv_bfloat16* __restrict__ B, long long b_hs, int b_ks,
-                    int b_ns, __nv_bfloat16* __restrict__ C, int ldc, int c_hs, const __nv_bfloat16* __restrict__ gate, int ldg, int M,
-                    int N, int K) {
+                    int b_ns, __nv_bfloat16* __restrict__ C, int ldc, int c_hs, const __nv_bfloat16* __restrict__ gate, int ldg, int g_hs,
+                    int g_ns, int M, int N, int K) {
     pdl_trigger();
     pdl_wait();
     __shared__ TileSmem sm;
@@ -156,13 +160,15 @@ head_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, int lda, int a_hs, cons
             const int m = m0 + tile_row(i, x);
             if (m >= M) continue;
             float g = 1.f;
-            if (gate) g = 1.f / (1.f + expf(-to_f32(gate[static_cast<size_t>(m) * ldg + a])));
+            if (gate && !g_ns) g = 1.f / (1.f + expf(-to_f32(gate[static_cast<size_t>(m) * ldg + static_cast<size_t>(a) * g_hs])));
 #pragma unroll
             for (int j = 0; j < 4; ++j)
 #pragma unroll
                 for (int y = 0; y < 2; ++y) {
                     const int n = n0 + tile_col(j, x + y);
-                    if (n < N) C[static_cast<size_t>(m) * ldc + static_cast<size_t>(a) * c_hs + n] = __float2bfloat16_rn(acc[i][j][x + y] * g);
+                    if (n >= N) continue;
+                    if (gate && g_ns) g = 1.f / (1.f + expf(-to_f32(gate[static_cast<size_t>(m) * ldg + static_cast<size_t>(a) * g_hs + static_cast<size_t>(n) * g_ns])));
+                    C[static_cast<size_t>(m) * ldc + static_cast<size_t>(a) * c_hs + n] = __float2bfloat16_rn(acc[i][j][x + y] * g);
                 }
         }
 }
@@ -210,7 +216,7 @@ __global__ void __launch_bounds__(kLatWarps * 32)
 latent_attention_kernel(const T* __restrict__ qa, T* __restrict__ out, const T* __restrict__ latent_pages,
                         const T* __restrict__ krot_pages, const int32_t* __restrict__ block_table, int table_width,
                         const int32_t* __restrict__ seq_of_token, const int32_t* __restrict__ positions, int heads, int rank,
-                        int rot, int page_size, float scale) {
+                        int rot, int page_size, float scale, const float* __restrict__ sinks) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float q_smem[];
@@ -265,7 +271,12 @@ latent_attention_kernel(const T* __restrict__ qa, T* __restrict__ out, const T* 
         }
         m = m_new;
     }
-    const float inv = 1.f / l;
+    float inv = 1.f / l;
+    if (sinks) {        // exp(sink_h) joins the denominator after the last key group: the order of the sums depends on the position only
+        const float sink = sinks[head], top = fmaxf(m, sink);
+        const float keep = expf(m - top);
+        inv = keep / (l * keep + expf(sink - top));
+    }
 #pragma unroll
     for (int i = 0; i < kMaxRank / 32; ++i) {
         const int d = lane + 32 * i;
@@ -279,21 +290,22 @@ using namespace stride;
 
 extern "C" {
 
-int stride_latent_prepare(const void* proj, int ld, int q_off, int kv_off, void* qa, const int32_t* positions,
+int stride_latent_prepare(const void* q, int ldq, const void* proj, int ld, int kv_off, void* qa, const int32_t* positions,
                           const int32_t* seq_of_token, const int32_t* slot_mapping, const float* cos_table, const float* sin_table,
                           const float* latent_w, float eps, void* latent_pages, void* krot_pages, int tokens, int heads, int dim,
                           int rot, int rot_dims, int rank, int dtype, cudaStream_t stream) {
-    if (tokens < 0 || heads <= 0 || dim <= 0 || rot < 0 || rank <= 0 || rot_dims < 0 || rot_dims > rot || rot_dims % 2 || ld <= 0 || q_off < 0)
+    if (tokens < 0 || heads <= 0 || dim <= 0 || rot < 0 || rank <= 0 || rot_dims < 0 || rot_dims > rot || rot_dims % 2 || ld <= 0 || ldq <= 0 || !q)
         return STRIDE_BAD_ARGUMENT;
     if (kv_off >= 0 && (!latent_w || !latent_pages || (rot > 0 && !krot_pages))) return STRIDE_BAD_ARGUMENT;
     if (tokens == 0) return 0;
     if (dtype == STRIDE_DTYPE_F32)
-        stride::launch(latent_prepare_kernel<float>, dim3(tokens), dim3(128), 0, stream, static_cast<const float*>(proj), ld, q_off, kv_off,
+        stride::launch(latent_prepare_kernel<float>, dim3(tokens), dim3(128), 0, stream, static_cast<const float*>(q), ldq,
+                       static_cast<const float*>(proj), ld, kv_off,
                        static_cast<float*>(qa), positions, seq_of_token, slot_mapping, cos_table, sin_table, latent_w, eps,
                        static_cast<float*>(latent_pages), static_cast<float*>(krot_pages), heads, dim, rot, rot_dims, rank);
     else if (dtype == STRIDE_DTYPE_BF16)
-        stride::launch(latent_prepare_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(proj), ld,
-                       q_off, kv_off, static_cast<__nv_bfloat16*>(qa), positions, seq_of_token, slot_mapping, cos_table, sin_table,
+        stride::launch(latent_prepare_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(q), ldq,
+                       static_cast<const __nv_bfloat16*>(proj), ld, kv_off, static_cast<__nv_bfloat16*>(qa), positions, seq_of_token, slot_mapping, cos_table, sin_table,
                        latent_w, eps, static_cast<__nv_bfloat16*>(latent_pages), static_cast<__nv_bfloat16*>(krot_pages), heads, dim,
                        rot, rot_dims, rank);
     else
@@ -302,20 +314,20 @@ int stride_latent_prepare(const void* proj, int ld, int q_off, int kv_off, void*
 }
 
 int stride_head_gemm(const void* A, int lda, int a_hs, const void* B, long long b_hs, int b_ks, int b_ns, void* C, int ldc, int c_hs,
-                     const void* gate, int ldg, int M, int heads, int N, int K, int dtype, cudaStream_t stream) {
-    if (M < 0 || heads <= 0 || N <= 0 || K <= 0 || heads > 65535) return STRIDE_BAD_ARGUMENT;
+                     const void* gate, int ldg, int g_hs, int g_ns, int M, int heads, int N, int K, int dtype, cudaStream_t stream) {
+    if (M < 0 || heads <= 0 || N <= 0 || K <= 0 || heads > 65535 || g_hs < 0 || g_ns < 0) return STRIDE_BAD_ARGUMENT;
     if (M == 0) return 0;
     const dim3 grid((N + HN - 1) / HN, heads, (M + HM - 1) / HM);
     if (grid.z > 65535) return STRIDE_UNSUPPORTED;
     if (dtype == STRIDE_DTYPE_F32)
         stride::launch(head_gemm_kernel<float>, grid, dim3(256), 0, stream, static_cast<const float*>(A), lda, a_hs,
                        static_cast<const float*>(B), b_hs, b_ks, b_ns, static_cast<float*>(C), ldc, c_hs, static_cast<const float*>(gate),
-                       ldg, M, N, K);
+                       ldg, g_hs, g_ns, M, N, K);
     else if (dtype == STRIDE_DTYPE_BF16) {
         const dim3 tc_grid((N + TN - 1) / TN, heads, (M + TM - 1) / TM);
         stride::launch(head_gemm_tc_kernel, tc_grid, dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(A), lda, a_hs,
                        static_cast<const __nv_bfloat16*>(B), b_hs, b_ks, b_ns, static_cast<__nv_bfloat16*>(C), ldc, c_hs,
-                       static_cast<const __nv_bfloat16*>(gate), ldg, M, N, K);
+                       static_cast<const __nv_bfloat16*>(gate), ldg, g_hs, g_ns, M, N, K);
     }
     else
         return STRIDE_BAD_ARGUMENT;
@@ -324,7 +336,7 @@ int stride_head_gemm(const void* A, int lda, int a_hs, const void* B, long long 
 
 int stride_latent_attention(const void* qa, void* out, const void* latent_pages, const void* krot_pages, const int32_t* block_table,
                             int table_width, const int32_t* seq_of_token, const int32_t* positions, int tokens, int heads, int rank,
-                            int rot, int page_size, float scale, int dtype, cudaStream_t stream) {
+                            int rot, int page_size, float scale, const float* sinks, int dtype, cudaStream_t stream) {
     if (tokens < 0 || heads <= 0 || rank <= 0 || rot < 0 || page_size <= 0 || table_width <= 0) return STRIDE_BAD_ARGUMENT;
     if (rank > kMaxRank) return STRIDE_UNSUPPORTED;
     if (tokens == 0) return 0;
@@ -334,12 +346,12 @@ int stride_latent_attention(const void* qa, void* out, const void* latent_pages,
     if (dtype == STRIDE_DTYPE_F32)
         stride::launch(latent_attention_kernel<float>, grid, dim3(kLatWarps * 32), smem, stream, static_cast<const float*>(qa),
                        static_cast<float*>(out), static_cast<const float*>(latent_pages), static_cast<const float*>(krot_pages), block_table,
-                       table_width, seq_of_token, positions, heads, rank, rot, page_size, scale);
+                       table_width, seq_of_token, positions, heads, rank, rot, page_size, scale, sinks);
     else if (dtype == STRIDE_DTYPE_BF16)
         stride::launch(latent_attention_kernel<__nv_bfloat16>, grid, dim3(kLatWarps * 32), smem, stream,
                        static_cast<const __nv_bfloat16*>(qa), static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(latent_pages),
                        static_cast<const __nv_bfloat16*>(krot_pages), block_table, table_width, seq_of_token, positions, heads, rank, rot,
-                       page_size, scale);
+                       page_size, scale, sinks);
     else
         return STRIDE_BAD_ARGUMENT;
     return STRIDE_LAUNCH_STATUS();

@@ -14,6 +14,8 @@
 // MT = 4 with 8 warps serves portions (64 rows = 64 / heads tokens), MT = 1 with 4 warps single tokens, where the keys
 // may be split over CTAs: a split leaves (max, sum, unnormalised O) per row in scratch and a second kernel merges them in
 // the order of the splits. A row's keys end at its token's position; the result of a row depends on its own keys only.
+// An optional sink per head (`sinks`, float32 [heads]) adds exp(sink) to a row's denominator, after the last key (in the
+// merge when the keys are split).
 // Sizes: rank and rot multiples of 16, rank <= 512, rank + rot <= 640.
 #include "common.cuh"
 
@@ -65,7 +67,7 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ qa, __nv_bfloat16* 
                            const __nv_bfloat16* __restrict__ latent_pages, const __nv_bfloat16* __restrict__ krot_pages,
                            const int32_t* __restrict__ block_table, int table_width, const int32_t* __restrict__ q_start,
                            const int32_t* __restrict__ q_len, const int32_t* __restrict__ ctx_len, int first_seq, int heads, int rank,
-                           int rot, int page_size, float scale, int splits, int keys_per_split) {
+                           int rot, int page_size, float scale, int splits, int keys_per_split, const float* __restrict__ sinks) {
     constexpr int ROWS = MT * 16;
     constexpr int KW = KT / NW;                    // keys a warp scores
     constexpr int SN = KW / 8;                     // n8 tiles of S a warp
@@ -249,7 +251,12 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ qa, __nv_bfloat16* 
             if (row >= total_rows) continue;
             const size_t grow = static_cast<size_t>(start) * heads + row;
             if (splits == 1) {
-                const float inv = 1.f / l_run[i][h];
+                float inv = 1.f / l_run[i][h];
+                if (sinks) {            // exp(sink) joins the sum; both terms relative to the larger of the maximum and the sink
+                    const float sink = sinks[row % heads], top = fmaxf(m_run[i][h], sink);
+                    const float keep = expf(m_run[i][h] - top);
+                    inv = keep / (l_run[i][h] * keep + expf(sink - top));
+                }
 #pragma unroll
                 for (int j = 0; j < MAXT; ++j) {
                     const int tile = warp + j * NW;
@@ -280,7 +287,7 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ qa, __nv_bfloat16* 
 // columns are independent loads and multiply-adds.
 __global__ void __launch_bounds__(128)
 latent_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ seq_of_token,
-                    int first_token, int rows, int heads, int rank, int splits) {
+                    int first_token, int rows, int heads, int rank, int splits, const float* __restrict__ sinks) {
     pdl_trigger();
     pdl_wait();
     const int r = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -300,7 +307,12 @@ latent_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict
         const float ws = __shfl_sync(0xffffffffu, s2 < 32 ? w0 : w1, s2 & 31), ls = __shfl_sync(0xffffffffu, s2 < 32 ? l0 : l1, s2 & 31);
         l = fmaf(ls, ws, l);
     }
-    const float inv = 1.f / l;
+    float inv = 1.f / l;
+    if (sinks) {
+        const float sink = sinks[r % heads], top = fmaxf(m, sink);
+        const float keep = expf(m - top);
+        inv = keep / (l * keep + expf(sink - top));
+    }
     w0 *= inv;
     w1 *= inv;
     for (int d = lane; d < rank; d += 32) {
@@ -338,7 +350,7 @@ int stride_latent_attention_tc(const void* qa, void* out, float* partial, const 
                                const int32_t* block_table, int table_width, const int32_t* q_start, const int32_t* q_len,
                                const int32_t* ctx_len, const int32_t* seq_of_token, int first_seq, int num_seqs, int first_token,
                                int tokens, int max_q_len, int heads, int rank, int rot, int page_size, float scale, int splits,
-                               int keys_per_split, cudaStream_t stream) {
+                               int keys_per_split, const float* sinks, cudaStream_t stream) {
     if (num_seqs < 0 || tokens < 0 || max_q_len <= 0 || page_size <= 0 || table_width <= 0 || splits <= 0) return STRIDE_BAD_ARGUMENT;
     if (!stride_latent_tc_supported(heads, rank, rot)) return STRIDE_UNSUPPORTED;
     if (splits > 1 && (!partial || keys_per_split <= 0 || keys_per_split % KT)) return STRIDE_BAD_ARGUMENT;
@@ -361,7 +373,7 @@ int stride_latent_attention_tc(const void* qa, void* out, float* partial, const 
         }
         const dim3 grid(static_cast<unsigned>((max_rows + 15) / 16), num_seqs, splits);
         stride::launch(kernel, grid, dim3(128), smem, stream, q, o, partial, lp, kp, block_table, table_width, q_start, q_len, ctx_len,
-                       first_seq, heads, rank, rot, page_size, scale, splits, kps);
+                       first_seq, heads, rank, rot, page_size, scale, splits, kps, splits == 1 ? sinks : nullptr);
     } else {
         if (splits != 1) return STRIDE_BAD_ARGUMENT;
         auto kernel = latent_attention_tc_kernel<4, 8>;
@@ -374,13 +386,13 @@ int stride_latent_attention_tc(const void* qa, void* out, float* partial, const 
         }
         const dim3 grid(static_cast<unsigned>((max_rows + 63) / 64), num_seqs, 1);
         stride::launch(kernel, grid, dim3(256), smem, stream, q, o, partial, lp, kp, block_table, table_width, q_start, q_len, ctx_len,
-                       first_seq, heads, rank, rot, page_size, scale, 1, kps);
+                       first_seq, heads, rank, rot, page_size, scale, 1, kps, sinks);
     }
     int status = STRIDE_LAUNCH_STATUS();
     if (status != 0 || splits == 1) return status;
     const int rows = tokens * heads;
     stride::launch(latent_merge_kernel, dim3((rows + 3) / 4), dim3(128), 0, stream, static_cast<const float*>(partial), o, seq_of_token,
-                   first_token, rows, heads, rank, splits);
+                   first_token, rows, heads, rank, splits, sinks);
     return STRIDE_LAUNCH_STATUS();
 }
 

@@ -157,7 +157,8 @@ shift_mix_kernel(const T* __restrict__ x, const float* __restrict__ mu, float* _
 // ------------------------------------------------------------------------------------------------ head_norm_gate
 // o [tokens, H, DV] float32 -> out [tokens, H * DV] (compute type): o / sqrt(mean(o^2) + eps) * weight * gate.
 // weight [.. ] float32 read at h * w_head_stride + j (0: one weight for all heads). gate_kind 0: sigmoid of float32
-// gate[t * ld_gate + h * DV + j]; 1: silu of a compute-type gate at the same place. One warp a (token, head).
+// gate[t * ld_gate + h * DV + j]; 1: silu of a compute-type gate at the same place; 2: sigmoid of a compute-type gate.
+// One warp a (token, head).
 template <typename T>
 __global__ void __launch_bounds__(256)
 head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ weight, int w_head_stride, const void* __restrict__ gate,
@@ -175,7 +176,9 @@ head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ wei
     const float inv = 1.f / sqrtf(ss / static_cast<float>(DV) + eps);
     for (int j = lane; j < DV; j += 32) {
         const size_t at = static_cast<size_t>(t) * ld_gate + h * DV + j;
-        const float g = gate_kind == 0 ? sigmoid_f(static_cast<const float*>(gate)[at]) : silu_f(to_f32(static_cast<const T*>(gate)[at]));
+        const float g = gate_kind == 0   ? sigmoid_f(static_cast<const float*>(gate)[at])
+                        : gate_kind == 1 ? silu_f(to_f32(static_cast<const T*>(gate)[at]))
+                                         : sigmoid_f(to_f32(static_cast<const T*>(gate)[at]));
         out[(static_cast<size_t>(t) * H + h) * DV + j] = from_f32<T>(row[j] * inv * weight[h * w_head_stride + j] * g);
     }
 }
@@ -742,7 +745,7 @@ int stride_shift_mix(const void* x, const float* mu, float* state, long long sta
 
 int stride_head_norm_gate(const float* o, const float* weight, int w_head_stride, const void* gate, int ld_gate, int gate_kind, void* out,
                           int tokens, int H, int DV, float eps, int dtype, cudaStream_t stream) {
-    if (tokens < 0 || H <= 0 || DV <= 0 || gate_kind < 0 || gate_kind > 1) return STRIDE_BAD_ARGUMENT;
+    if (tokens < 0 || H <= 0 || DV <= 0 || gate_kind < 0 || gate_kind > 2) return STRIDE_BAD_ARGUMENT;
     if (tokens == 0) return 0;
     const long long pairs = static_cast<long long>(tokens) * H;
     const dim3 grid(static_cast<unsigned>((pairs + 7) / 8)), block(256);

@@ -6,7 +6,9 @@
 //   moe_select_sigmoid  the choice by another rule: scores s = sigmoid(z); choice scores c = s + correction; the experts form
 //                 equal groups of neighbours, a group's score is the sum of its two largest c, only the experts of the
 //                 `keep` best groups can be chosen (the others count as minus infinity); the `top` largest c win (the
-//                 lower index among equals); weights s / (sum of the chosen s + 1e-20) * route_scale;
+//                 lower index among equals); weights s / (sum of the chosen s + 1e-20) * route_scale. `rule` bits change
+//                 it: 1 makes s the softmax of z over all experts, 2 makes a group's score its largest c, 4 leaves the
+//                 weights at s * route_scale (no division by their sum);
 //   moe_plan      one CTA counts the rows of every expert, lays the (token, choice) pairs out expert by expert and
 //                 writes where each pair went: `offsets` [experts + 1], `perm_token` [rows] and `row_of` [tokens, top];
 //   grouped_gemm  C[p, :] = act(A[src(p), :] W[e(p)]^T) for the rows p of every expert e, the tiles of all experts in
@@ -15,6 +17,7 @@
 //                 operands, tensor-core tiles (mma_tile.cuh) for bfloat16;
 //                 act 1 squares the positive part; act 2 reads W's rows as (gate, up) pairs, row 2i beside row 2i + 1,
 //                 and writes g' sigmoid(alpha g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit), N / 2 wide;
+//                 act 3 reads the same pairs and writes g sigmoid(g) u;
 //   moe_combine   out[t] = sum_k weight[t, k] * Y[row_of[t, k]] (+ a shared expert's output, optionally times the
 //                 sigmoid of a per-token logit), in the order of k.
 // A row's result depends only on that row: not on the batch, nor on where the plan put it.
@@ -25,6 +28,7 @@ namespace stride {
 
 constexpr int kMaxExperts = 256;
 constexpr int kMaxTop = 32;
+constexpr int kRuleSoftmax = 1, kRuleGroupMax = 2, kRuleKeepScores = 4;      // bits of the group router's `rule`
 
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -144,7 +148,7 @@ moe_select_kernel(const float* __restrict__ logits, const float* __restrict__ bi
 __global__ void __launch_bounds__(128)
 moe_select_sigmoid_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ correction,
                           const int32_t* __restrict__ seq_of_token, int32_t* __restrict__ ids, float* __restrict__ weights, int tokens,
-                          int experts, int top, int groups, int keep, float route_scale) {
+                          int experts, int top, int groups, int keep, float route_scale, int rule) {
     pdl_trigger();
     pdl_wait();
     __shared__ float choice_s[4][kMaxExperts];
@@ -162,13 +166,39 @@ moe_select_sigmoid_kernel(const float* __restrict__ logits, int ld, const float*
     float* choice = choice_s[warp];
     float* gscore = group_s[warp];
     float score[kMaxExperts / 32];       // lane holds experts lane, lane + 32, ...
+    if (rule & kRuleSoftmax) {           // softmax over all experts: largest logit, exponentials, their sum in a fixed order
+        float top_z = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < kMaxExperts / 32; ++i) {
-        const int e = i * 32 + lane;
-        score[i] = 0.f;
-        if (e < experts) {
-            score[i] = 1.f / (1.f + expf(-logits[static_cast<size_t>(t) * ld + e]));
-            choice[e] = score[i] + (correction ? correction[e] : 0.f);
+        for (int i = 0; i < kMaxExperts / 32; ++i) {
+            const int e = i * 32 + lane;
+            score[i] = e < experts ? logits[static_cast<size_t>(t) * ld + e] : -INFINITY;
+            top_z = fmaxf(top_z, score[i]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) top_z = fmaxf(top_z, __shfl_xor_sync(0xffffffffu, top_z, o));
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < kMaxExperts / 32; ++i) {
+            score[i] = i * 32 + lane < experts ? expf(score[i] - top_z) : 0.f;
+            sum += score[i];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+#pragma unroll
+        for (int i = 0; i < kMaxExperts / 32; ++i) {
+            const int e = i * 32 + lane;
+            score[i] /= sum;
+            if (e < experts) choice[e] = score[i] + (correction ? correction[e] : 0.f);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < kMaxExperts / 32; ++i) {
+            const int e = i * 32 + lane;
+            score[i] = 0.f;
+            if (e < experts) {
+                score[i] = 1.f / (1.f + expf(-logits[static_cast<size_t>(t) * ld + e]));
+                choice[e] = score[i] + (correction ? correction[e] : 0.f);
+            }
         }
     }
     __syncwarp();
@@ -181,7 +211,7 @@ moe_select_sigmoid_kernel(const float* __restrict__ logits, int ld, const float*
                 if (c > a) { b = a; a = c; }
                 else if (c > b) b = c;
             }
-            gscore[g] = size > 1 ? a + b : a;
+            gscore[g] = (size > 1 && !(rule & kRuleGroupMax)) ? a + b : a;
         }
         __syncwarp();
         unsigned kept[kMaxExperts / 32] = {};           // bit l of kept[i]: group i * 32 + l stays
@@ -243,7 +273,7 @@ moe_select_sigmoid_kernel(const float* __restrict__ logits, int ld, const float*
     }
     if (lane < top) {
         ids[static_cast<size_t>(t) * top + lane] = mine_id;
-        weights[static_cast<size_t>(t) * top + lane] = mine / (denom + 1e-20f) * route_scale;
+        weights[static_cast<size_t>(t) * top + lane] = (rule & kRuleKeepScores) ? mine * route_scale : mine / (denom + 1e-20f) * route_scale;
     }
 }
 
@@ -288,6 +318,11 @@ __device__ __forceinline__ float clamped_gated(float g, float u, float limit, fl
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
     return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+}
+
+// What a (gate, up) pair becomes: act 2 the clamped form, act 3 plain SiLU(g) * u.
+__device__ __forceinline__ float gated_pair(int act, float g, float u, float limit, float alpha) {
+    return act == 3 ? g / (1.f + expf(-g)) * u : clamped_gated(g, u, limit, alpha);
 }
 
 // Tiles of GM x GN outputs; tile `blockIdx.y` belongs to the expert whose tiles it falls among.
@@ -350,11 +385,11 @@ grouped_gemm_kernel(const TA* __restrict__ A, int lda, const int32_t* __restrict
     for (int i = 0; i < 4; ++i) {
         const int m = m0 + ty * 4 + i;
         if (m >= m_end) continue;
-        if (act == 2) {                     // columns come in (gate, up) pairs
+        if (act >= 2) {                     // columns come in (gate, up) pairs
 #pragma unroll
             for (int j = 0; j < 4; j += 2) {
                 const int n = n0 + tx * 4 + j;
-                if (n + 1 < N) C[static_cast<size_t>(m) * ldc + n / 2] = from_f32<TC>(clamped_gated(acc[i][j], acc[i][j + 1], limit, alpha));
+                if (n + 1 < N) C[static_cast<size_t>(m) * ldc + n / 2] = from_f32<TC>(gated_pair(act, acc[i][j], acc[i][j + 1], limit, alpha));
             }
             continue;
         }
@@ -409,9 +444,9 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int32
             for (int x = 0; x < 4; ++x) {
                 const int m = m0 + tile_row(i, x), n = n0 + tile_col(j, x);
                 if (m >= m_end || n >= N) continue;
-                if (act == 2) {             // elements 0 and 2 of a fragment are gates, their neighbours the ups
+                if (act >= 2) {             // elements 0 and 2 of a fragment are gates, their neighbours the ups
                     if (!(x & 1) && n + 1 < N)
-                        C[static_cast<size_t>(m) * ldc + n / 2] = from_f32<TC>(clamped_gated(acc[i][j][x], acc[i][j][x + 1], limit, alpha));
+                        C[static_cast<size_t>(m) * ldc + n / 2] = from_f32<TC>(gated_pair(act, acc[i][j][x], acc[i][j][x + 1], limit, alpha));
                     continue;
                 }
                 float v = acc[i][j][x];
@@ -486,16 +521,22 @@ int stride_moe_select(const float* logits, const float* bias, const int32_t* seq
     return STRIDE_LAUNCH_STATUS();
 }
 
-int stride_moe_select_sigmoid(const float* logits, int ld, const float* correction, const int32_t* seq_of_token, int32_t* ids,
-                              float* weights, int tokens, int experts, int top, int groups, int keep, float route_scale, cudaStream_t stream) {
+int stride_moe_select_groups(const float* logits, int ld, const float* correction, const int32_t* seq_of_token, int32_t* ids,
+                             float* weights, int tokens, int experts, int top, int groups, int keep, float route_scale, int rule,
+                             cudaStream_t stream) {
     if (tokens < 0 || experts <= 0 || top <= 0 || top > experts || ld < experts || groups <= 0 || keep <= 0 || keep > groups ||
-        experts % groups || top > keep * (experts / groups))
+        experts % groups || top > keep * (experts / groups) || rule < 0 || rule > 7)
         return STRIDE_BAD_ARGUMENT;
     if (experts > kMaxExperts || top > kMaxTop) return STRIDE_UNSUPPORTED;
     if (tokens == 0) return 0;
     stride::launch(moe_select_sigmoid_kernel, dim3((tokens + 3) / 4), dim3(128), 0, stream, logits, ld, correction, seq_of_token, ids, weights,
-                   tokens, experts, top, groups, keep, route_scale);
+                   tokens, experts, top, groups, keep, route_scale, rule);
     return STRIDE_LAUNCH_STATUS();
+}
+
+int stride_moe_select_sigmoid(const float* logits, int ld, const float* correction, const int32_t* seq_of_token, int32_t* ids,
+                              float* weights, int tokens, int experts, int top, int groups, int keep, float route_scale, cudaStream_t stream) {
+    return stride_moe_select_groups(logits, ld, correction, seq_of_token, ids, weights, tokens, experts, top, groups, keep, route_scale, 0, stream);
 }
 
 int stride_moe_plan(const int32_t* ids, int tokens, int top, int experts, int32_t* offsets, int32_t* perm_token, int32_t* row_of,
@@ -510,7 +551,8 @@ int stride_moe_plan(const int32_t* ids, int tokens, int top, int experts, int32_
 // tensor cores); 3 = as 2 on the FMA kernel.
 int stride_grouped_gemm(const void* A, int lda, const int32_t* row_map, const void* W, const int32_t* offsets, int experts, void* C,
                         int ldc, int max_rows, int N, int K, int act, float limit, float alpha, int kind, cudaStream_t stream) {
-    if (max_rows < 0 || experts <= 0 || N <= 0 || K <= 0 || lda < K || ldc < (act == 2 ? N / 2 : N) || (act == 2 && N % 2)) return STRIDE_BAD_ARGUMENT;
+    if (max_rows < 0 || experts <= 0 || N <= 0 || K <= 0 || lda < K || act < 0 || act > 3 || ldc < (act >= 2 ? N / 2 : N) || (act >= 2 && N % 2))
+        return STRIDE_BAD_ARGUMENT;
     if (max_rows == 0) return 0;
     const int max_tiles = (max_rows + GM - 1) / GM + experts;       // no expert has more than one ragged tile
     if (max_tiles > 65535) return STRIDE_UNSUPPORTED;

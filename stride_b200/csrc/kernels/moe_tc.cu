@@ -12,7 +12,8 @@
 // Two CTAs fit one SM, so one tile's epilogue runs under the other's products.
 //
 // act 0: none; 1: the square of the positive part; 2: the rows of W come as (gate, up) pairs, row 2i beside row
-// 2i + 1, and the tile leaves g' sigmoid(alpha g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit), N / 2 wide.
+// 2i + 1, and the tile leaves g' sigmoid(alpha g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit), N / 2 wide;
+// 3: the same pairs, and the tile leaves g sigmoid(g) u.
 //
 // gather_rows lays the rows of the step's tokens out expert by expert first (xs[p] = x[perm[p]]), so that the first
 // product's A operand is one matrix a tensor map can describe; the second product's input is in that order already.
@@ -132,7 +133,7 @@ grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         const bool ok = mbar_wait(smem_u32(&done_bar), 0, status, 13);
         tc_fence_after();
         if (ok) {
-            const int width = act == 2 ? N / 2 : N;
+            const int width = act >= 2 ? N / 2 : N;
             OutT* crow = C + static_cast<size_t>(m) * ldc;
 #pragma unroll 1
             for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
@@ -140,11 +141,16 @@ grouped_gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 float v[32];
                 tmem_ld32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + c0, v);
                 if (m >= m_end) continue;
-                if (act == 2) {
+                if (act >= 2) {
                     const int col = (n0 + c0) / 2;
                     float r[16];
+                    if (act == 3) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) r[j] = act_clamped(v[2 * j], v[2 * j + 1], limit, alpha);
+                        for (int j = 0; j < 16; ++j) r[j] = v[2 * j] / (1.f + expf(-v[2 * j])) * v[2 * j + 1];
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) r[j] = act_clamped(v[2 * j], v[2 * j + 1], limit, alpha);
+                    }
                     if (vec_ok && col + 16 <= width) {
 #pragma unroll
                         for (int j = 0; j < 16; j += 4) store4(crow + col + j, r + j);
@@ -225,11 +231,11 @@ using namespace stride;
 extern "C" {
 
 // C[p] = act(A[p] @ W[e(p)]^T) for rows lying expert by expert. A: [max_rows, K] bf16 with row stride lda, W: [experts, N, K] bf16,
-// C: [max_rows, N] (N / 2 with act 2), bf16 or float32. Returns -2 for what it does not take (K or lda not a multiple of
+// C: [max_rows, N] (N / 2 with act 2 and 3), bf16 or float32. Returns -2 for what it does not take (K or lda not a multiple of
 // 8, unaligned operands); the caller then uses the other grouped product.
 int stride_grouped_gemm_tc5(const void* A, int lda, const void* W, const int32_t* offsets, int experts, void* C, int ldc, int max_rows, int N,
                             int K, int act, float limit, float alpha, int out_is_f32, int* status, cudaStream_t stream) {
-    if (max_rows < 0 || experts <= 0 || N <= 0 || K <= 0 || lda < K || act < 0 || act > 2 || ldc < (act == 2 ? N / 2 : N) || (act == 2 && N % 2))
+    if (max_rows < 0 || experts <= 0 || N <= 0 || K <= 0 || lda < K || act < 0 || act > 3 || ldc < (act >= 2 ? N / 2 : N) || (act >= 2 && N % 2))
         return STRIDE_BAD_ARGUMENT;
     if (status == nullptr) return STRIDE_BAD_ARGUMENT;
     if (max_rows == 0) return 0;

@@ -12,6 +12,9 @@
 //   softcap       x = c tanh(x / c)            (float32, in place: logits)
 //   tanh_inplace  x = tanh(x)
 //   weighted_sum  out = sa * a + sb * b        (the sum of two branches; out may be a or b)
+//   stream_concat out[t] = [x[t] rounded to the compute dtype | y[t]]: the float32 stream beside a second input, as the
+//                 operand of one product over both
+//   add_row_vector x[t, :] += b for every live row (float32)
 #include "common.cuh"
 
 namespace stride {
@@ -250,6 +253,28 @@ int gated(const void* in, void* out, int tokens, int inter, int block, int act, 
     return STRIDE_LAUNCH_STATUS();
 }
 
+template <typename T>
+__global__ void stream_concat_kernel(const float* __restrict__ x, const T* __restrict__ y, T* __restrict__ out, int width, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / (2 * static_cast<size_t>(width));
+    const int c = static_cast<int>(i - t * 2 * width);
+    out[i] = c < width ? from_f32<T>(x[t * width + c]) : y[t * width + (c - width)];
+}
+
+__global__ void add_row_vector_kernel(float* __restrict__ x, const float* __restrict__ b, const int32_t* __restrict__ seq_of_token, int width,
+                                      size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / width;
+    if (seq_of_token && seq_of_token[t] < 0) return;
+    x[i] = __fadd_rn(x[i], b[i - t * width]);
+}
+
 }  // namespace stride
 
 using namespace stride;
@@ -319,6 +344,30 @@ int stride_pointwise(void* x, const void* g, int op, float cap, long long n, int
     if (dtype == STRIDE_DTYPE_F32) return unary<float>(x, g, op, cap, n, stream);
     if (dtype == STRIDE_DTYPE_BF16) return unary<__nv_bfloat16>(x, g, op, cap, n, stream);
     return STRIDE_BAD_ARGUMENT;
+}
+
+int stride_stream_concat(const float* x, const void* y, void* out, int tokens, int width, int dtype, cudaStream_t stream) {
+    if (tokens < 0 || width <= 0) return STRIDE_BAD_ARGUMENT;
+    if (tokens == 0) return 0;
+    const size_t total = static_cast<size_t>(tokens) * 2 * width;
+    const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+    if (dtype == STRIDE_DTYPE_F32)
+        stride::launch(stream_concat_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, static_cast<const float*>(y), static_cast<float*>(out),
+                       width, total);
+    else if (dtype == STRIDE_DTYPE_BF16)
+        stride::launch(stream_concat_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, x, static_cast<const __nv_bfloat16*>(y),
+                       static_cast<__nv_bfloat16*>(out), width, total);
+    else
+        return STRIDE_BAD_ARGUMENT;
+    return STRIDE_LAUNCH_STATUS();
+}
+
+int stride_add_row_vector(float* x, const float* b, const int32_t* seq_of_token, int tokens, int width, cudaStream_t stream) {
+    if (tokens < 0 || width <= 0) return STRIDE_BAD_ARGUMENT;
+    if (tokens == 0) return 0;
+    const size_t total = static_cast<size_t>(tokens) * width;
+    stride::launch(add_row_vector_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0, stream, x, b, seq_of_token, width, total);
+    return STRIDE_LAUNCH_STATUS();
 }
 
 int stride_weighted_sum(void* out, const void* a, float sa, const void* b, float sb, long long n, int dtype, cudaStream_t stream) {

@@ -8,6 +8,8 @@
 //                   added, each query and key head (width hd) and each value head (width vd) is divided by its own root
 //                   mean square (no weight; either norm can be switched off), written back in place, and keys and values
 //                   go to the token's place in the pages ([page, kv_head, slot, width]) when a slot mapping is given.
+//   rms_norm_cols   out[t] = x / sqrt(mean(x^2) + eps) * w for a column block x of a wider buffer (a latent between two
+//                   products): one warp a row, float32 statistics.
 // The order of every sum depends only on the row's width, never on the batch.
 #include "common.cuh"
 
@@ -283,6 +285,26 @@ qkv_unit_norm_vec_kernel(T* __restrict__ qkv, int row_stride, const float* __res
     }
 }
 
+// x: [rows, ld] from column 0 on (the caller offsets the pointer); out: [rows, ld_out]. One warp a row.
+template <typename T>
+__global__ void __launch_bounds__(128)
+rms_norm_cols_kernel(const T* __restrict__ x, int ld, const float* __restrict__ weight, T* __restrict__ out, int ld_out, int rows, int width,
+                     float eps) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r >= rows) return;
+    const T* src = x + static_cast<size_t>(r) * ld;
+    float sq = 0.f;
+    for (int i = lane; i < width; i += 32) {
+        const float v = to_f32(src[i]);
+        sq = fmaf(v, v, sq);
+    }
+    const float inv = rsqrtf(warp_sum(sq) / static_cast<float>(width) + eps);
+    T* dst = out + static_cast<size_t>(r) * ld_out;
+    for (int i = lane; i < width; i += 32) dst[i] = from_f32<T>(__fmul_rn(__fmul_rn(to_f32(src[i]), inv), weight[i]));
+}
+
 }  // namespace stride
 
 using namespace stride;
@@ -311,6 +333,22 @@ int stride_norm_add(float* residual, const void* delta, const float* bias, const
     } else {
         return STRIDE_BAD_ARGUMENT;
     }
+    return STRIDE_LAUNCH_STATUS();
+}
+
+int stride_rms_norm_cols(const void* x, int ld, const float* weight, void* out, int ld_out, int rows, int width, float eps, int dtype,
+                         cudaStream_t stream) {
+    if (rows < 0 || width <= 0 || ld < width || ld_out < width || !weight) return STRIDE_BAD_ARGUMENT;
+    if (rows == 0) return 0;
+    const dim3 grid((rows + 3) / 4);
+    if (dtype == STRIDE_DTYPE_F32)
+        stride::launch(rms_norm_cols_kernel<float>, grid, dim3(128), 0, stream, static_cast<const float*>(x), ld, weight, static_cast<float*>(out),
+                       ld_out, rows, width, eps);
+    else if (dtype == STRIDE_DTYPE_BF16)
+        stride::launch(rms_norm_cols_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(x), ld, weight,
+                       static_cast<__nv_bfloat16*>(out), ld_out, rows, width, eps);
+    else
+        return STRIDE_BAD_ARGUMENT;
     return STRIDE_LAUNCH_STATUS();
 }
 

@@ -88,16 +88,16 @@ _SIGNATURES = {
     "stride_add_scaled": ("dynamic_tanh", [c_void_p, c_void_p, c_float, c_longlong, c_int, c_void_p]),
     "stride_token_side": ("token_side", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                          c_int, c_int, c_float, c_float, c_int, c_void_p]),
-    "stride_latent_prepare": ("latent_attention", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+    "stride_latent_prepare": ("latent_attention", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                    c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                                    c_void_p]),
     "stride_head_gemm": ("latent_attention", [c_void_p, c_int, c_int, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
-                                              c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+                                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_latent_attention": ("latent_attention", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
-                                                     c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
+                                                     c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p]),
     "stride_latent_attention_tc": ("latent_attention_tc", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                                           c_float, c_int, c_int, c_void_p]),
+                                                           c_float, c_int, c_int, c_void_p, c_void_p]),
     "stride_side_gate": ("token_side", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
     "stride_side_norm_add": ("token_side", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p]),
     "stride_cast_rows": ("token_side", [c_void_p, c_void_p, c_longlong, c_int, c_void_p]),
@@ -127,6 +127,18 @@ _SIGNATURES = {
                                            c_float, c_int, c_int, c_int, c_void_p]),
     "stride_moe_select_sigmoid": ("moe", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                           c_void_p]),
+    "stride_moe_select_groups": ("moe", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                         c_int, c_void_p]),
+    "stride_stream_concat": ("pointwise", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "stride_add_row_vector": ("pointwise", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "stride_rms_norm_cols": ("unit_norm", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p]),
+    "stride_conv_head_norm": ("short_conv", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_void_p,
+                                             c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                             c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "stride_conv_tail": ("short_conv", [c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                        c_int, c_void_p]),
+    "stride_mlstm_scan": ("mlstm", [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p,
+                                    c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_pointwise": ("pointwise", [c_void_p, c_void_p, c_int, c_float, c_longlong, c_int, c_void_p]),
     "stride_weighted_sum": ("pointwise", [c_void_p, c_void_p, c_float, c_void_p, c_float, c_longlong, c_int, c_void_p]),
     "stride_delta_prepare": ("linear_recurrence", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong,
@@ -169,7 +181,7 @@ _CLASS_OF = {
     "stride_latent_prepare": "latent norm + rotation + cache write", "stride_head_gemm": "per-head product",
     "stride_latent_attention": "attention (latent, exact kernel)", "stride_latent_attention_tc": "attention (latent, tensor cores)",
     "stride_side_gate": "token side input", "stride_side_norm_add": "token side input", "stride_cast_rows": "token side input",
-    "stride_moe_select": "router", "stride_moe_select_sigmoid": "router", "stride_head_gate": "gates and caps",
+    "stride_moe_select": "router", "stride_moe_select_sigmoid": "router", "stride_moe_select_groups": "router", "stride_head_gate": "gates and caps",
     "stride_add_sinusoid": "embedding", "stride_norm_add": "norm", "stride_qkv_unit_norm": "head norms + cache write",
     "stride_rglru_conv": "recurrent block: convolution",
     "stride_rglru_gates": "recurrent block: gates", "stride_rglru_scan": "recurrent block: recurrence", "stride_rglru_scan_pieces": "recurrent block: recurrence", "stride_moe_route": "router",
@@ -179,6 +191,9 @@ _CLASS_OF = {
     "stride_delta_prepare": "delta rule: convolution, unit vectors, decay", "stride_delta_scan": "delta rule: recurrence",
     "stride_bonus_scan": "decayed memory: recurrence", "stride_shift_mix": "decayed memory: token shift",
     "stride_head_norm_gate": "per-head norm and gate",
+    "stride_stream_concat": "repeated block: input", "stride_add_row_vector": "repeated block: input",
+    "stride_rms_norm_cols": "latent norm", "stride_conv_head_norm": "convolution + head norms + cache write",
+    "stride_conv_tail": "convolution + head norms + cache write", "stride_mlstm_scan": "matrix LSTM: recurrence",
 }
 
 
@@ -513,12 +528,87 @@ def head_norm_gate(o, weight, per_head_weight: bool, gate, gate_kind: str, out, 
     [H * DV]; ``gate`` [tokens, >= gate_off + H * DV], read from column ``gate_off`` on: ``sigmoid`` of float32 values or
     ``silu`` of values in ``out``'s type."""
     tokens = o.shape[0]
-    kind = {"sigmoid": 0, "silu": 1}[gate_kind]
+    kind = {"sigmoid": 0, "silu": 1, "sigmoid_compute": 2}[gate_kind]      # the last: sigmoid of a gate in ``out``'s type
     _check(_fn("stride_head_norm_gate")(
         _dev(o, "o", torch.float32), _dev(weight, "weight", torch.float32), DV if per_head_weight else 0,
         _dev(gate, "gate", torch.float32 if kind == 0 else out.dtype) + gate_off * gate.element_size(), gate.shape[1], kind,
         _dev(out, "out"), tokens, H, DV, float(eps),
         _code(out.dtype), _stream()), "head_norm_gate")
+
+
+def mlstm_state_floats(H: int, D: int, DV: int) -> int:
+    return H * D * DV + H * D + H
+
+
+def mlstm_scan(proj, q_off: int, k_off: int, v_off: int, gates, bias_i, bias_f, cap: float, q_scale: float, o, state, q_start, q_len,
+               state_slot, num_seqs: int, H: int, D: int, DV: int) -> None:
+    """The matrix memory with exponential gates over every request of the step, in token order. ``proj`` [tokens, ld] holds
+    q, k ([H, D]) and v ([H, DV]) from the given columns on; ``gates`` (float32 [tokens, >= 2H]) the projections of the input
+    gates (columns 0..H-1) and the forget gates (H..2H-1), to which ``bias_i`` / ``bias_f`` are added before
+    ``cap * tanh(. / cap)``. ``o`` [tokens, H * DV] float32; ``state`` [slots, >= mlstm_state_floats]: S, n, m per head."""
+    if state.shape[1] < mlstm_state_floats(H, D, DV) or o.shape[1] != H * DV or gates.shape[1] < 2 * H:
+        raise KernelError("mlstm_scan: shapes do not agree")
+    _check(_fn("stride_mlstm_scan")(
+        _dev(proj, "proj"), proj.shape[1], int(q_off), int(k_off), int(v_off), _dev(gates, "gates", torch.float32), gates.shape[1],
+        _dev(bias_i, "bias_i", torch.float32), _dev(bias_f, "bias_f", torch.float32), float(cap), float(q_scale),
+        _dev(o, "o", torch.float32), _dev(state, "state", torch.float32), state.shape[1], _dev(q_start, "q_start", torch.int32),
+        _dev(q_len, "q_len", torch.int32), _dev(state_slot, "state_slot", torch.int32), int(num_seqs), H, D, DV, _code(proj.dtype),
+        _stream()), "mlstm_scan")
+
+
+# ------------------------------------------------------------ short convolution with head norms
+def conv_head_norm(raw, out, conv_w, state, tail_off: int, seq_of_token, q_start, state_slot, wq, wk, eps: float, slot_mapping, k_pages,
+                   v_pages, nq: int, nkv: int, hd: int, vd: int, page_size: int) -> None:
+    """From the fused projection ``raw`` [tokens, >= C] (query heads, key heads, value heads; C channels): the causal
+    convolution ``conv_w`` (float32 [C, taps], or None) over a request's projected rows, which before the step's first token
+    come from the tail in ``state`` (float32 [slots, n], rows [taps - 1, C] at ``tail_off``); then the RMS norm of every query
+    head with the weight ``wq`` and of every key head with ``wk`` (float32 [hd], or None for no norm); into ``out``, and with
+    ``slot_mapping`` keys and values into their pages. The tail is not moved: ``conv_tail`` does that afterwards."""
+    taps = 1 if conv_w is None else conv_w.shape[1]
+    if out.dtype != raw.dtype or out.shape[0] != raw.shape[0]:
+        raise KernelError("conv_head_norm: raw and out must agree in rows and element type")
+    _check(_fn("stride_conv_head_norm")(
+        _dev(raw, "raw"), raw.shape[1], _dev(out, "out"), out.shape[1], _opt(conv_w, "conv_w", torch.float32), taps,
+        _opt(state, "state", torch.float32), 0 if state is None else state.shape[1], int(tail_off),
+        _dev(seq_of_token, "seq_of_token", torch.int32), _dev(q_start, "q_start", torch.int32), _dev(state_slot, "state_slot", torch.int32),
+        _opt(wq, "wq", torch.float32), _opt(wk, "wk", torch.float32), float(eps), _opt(slot_mapping, "slot_mapping", torch.int32),
+        _opt(k_pages, "k_pages", raw.dtype), _opt(v_pages, "v_pages", raw.dtype), raw.shape[0], nq, nkv, hd, vd, page_size,
+        _code(raw.dtype), _stream()), "conv_head_norm")
+
+
+def conv_tail(raw, state, tail_off: int, q_start, q_len, state_slot, num_seqs: int, channels: int, taps: int) -> None:
+    """Moves every request's convolution tail on by the step's rows of ``raw`` (its first ``channels`` columns)."""
+    _check(_fn("stride_conv_tail")(
+        _dev(raw, "raw"), raw.shape[1], _dev(state, "state", torch.float32), state.shape[1], int(tail_off),
+        _dev(q_start, "q_start", torch.int32), _dev(q_len, "q_len", torch.int32), _dev(state_slot, "state_slot", torch.int32),
+        int(num_seqs), int(channels), int(taps), _code(raw.dtype), _stream()), "conv_tail")
+
+
+def rms_norm_cols(x, col_off: int, width: int, weight, out, eps: float) -> None:
+    """``out[t] = y / sqrt(mean(y^2) + eps) * weight`` for ``y = x[t, col_off : col_off + width]``; ``out`` [tokens, >= width]."""
+    if out.dtype != x.dtype or out.shape[0] != x.shape[0] or x.shape[1] < col_off + width or out.shape[1] < width or weight.numel() != width:
+        raise KernelError("rms_norm_cols: shapes do not agree")
+    _check(_fn("stride_rms_norm_cols")(_dev(x, "x") + int(col_off) * x.element_size(), x.shape[1], _dev(weight, "weight", torch.float32),
+                                       _dev(out, "out"), out.shape[1], x.shape[0], int(width), float(eps), _code(x.dtype), _stream()),
+           "rms_norm_cols")
+
+
+def stream_concat(residual, second, out) -> None:
+    """``out[t] = [residual[t] rounded to out's type | second[t]]`` ([tokens, 2 * hidden])."""
+    tokens, hidden = residual.shape
+    if second.shape != (tokens, hidden) or out.shape != (tokens, 2 * hidden) or second.dtype != out.dtype:
+        raise KernelError("stream_concat: shapes or element types do not agree")
+    _check(_fn("stride_stream_concat")(_dev(residual, "residual", torch.float32), _dev(second, "second"), _dev(out, "out"), tokens, hidden,
+                                       _code(out.dtype), _stream()), "stream_concat")
+
+
+def add_row_vector(residual, vector, seq_of_token=None) -> None:
+    """``residual[t] += vector`` (float32) for every row that is not padding."""
+    tokens, hidden = residual.shape
+    if vector.numel() != hidden:
+        raise KernelError("add_row_vector: the vector must have the rows' width")
+    _check(_fn("stride_add_row_vector")(_dev(residual, "residual", torch.float32), _dev(vector, "vector", torch.float32),
+                                        _opt(seq_of_token, "seq_of_token", torch.int32), tokens, hidden, _stream()), "add_row_vector")
 
 
 # ------------------------------------------------------------ Dynamic Tanh, scaled sums
@@ -576,16 +666,20 @@ def side_norm_add(residual, y, seq_of_token, norm_w, eps: float, scale: float) -
 
 # --------------------------------------------------------------- latent attention
 def latent_prepare(proj, q_off: int, kv_off: int, qa, positions, seq_of_token, slot_mapping, cos, sin, latent_w, eps: float,
-                   latent_pages, krot_pages, heads: int, dim: int, rot: int, rot_dims: int, rank: int) -> None:
+                   latent_pages, krot_pages, heads: int, dim: int, rot: int, rot_dims: int, rank: int, q=None) -> None:
     """From the projections of a step (``proj`` [tokens, ld]: queries at ``q_off``, the latent projection at ``kv_off``
     or ``kv_off`` < 0 for none): the rotated parts of the queries into ``qa`` [tokens, heads, rank + rot], and, when
-    there is a latent projection and ``slot_mapping``, the normed latent and the rotated key part into their pages."""
+    there is a latent projection and ``slot_mapping``, the normed latent and the rotated key part into their pages.
+    ``q`` [tokens, >= heads * (dim + rot)]: the queries in a buffer of their own instead of ``proj``'s columns."""
     tokens = proj.shape[0]
     if qa.shape != (tokens, heads * (rank + rot)) or qa.dtype != proj.dtype:
         raise KernelError("latent_prepare: qa must be [tokens, heads * (rank + rot)] of the projections' type")
+    if q is not None and (q.dtype != proj.dtype or q.shape[0] != tokens or q.shape[1] < heads * (dim + rot)):
+        raise KernelError("latent_prepare: q must be [tokens, >= heads * (dim + rot)] of the projections' type")
     has_kv = kv_off >= 0
+    q_ptr, ldq = (_dev(proj, "proj") + int(q_off) * proj.element_size(), proj.shape[1]) if q is None else (_dev(q, "q"), q.shape[1])
     _check(_fn("stride_latent_prepare")(
-        _dev(proj, "proj"), proj.shape[1], int(q_off), int(kv_off), _dev(qa, "qa"), _dev(positions, "positions", torch.int32),
+        q_ptr, ldq, _dev(proj, "proj"), proj.shape[1], int(kv_off), _dev(qa, "qa"), _dev(positions, "positions", torch.int32),
         _dev(seq_of_token, "seq_of_token", torch.int32), _opt(slot_mapping, "slot_mapping", torch.int32), _dev(cos, "cos", torch.float32),
         _dev(sin, "sin", torch.float32), _opt(latent_w if has_kv else None, "latent_w", torch.float32), float(eps),
         _opt(latent_pages if has_kv else None, "latent_pages", proj.dtype), _opt(krot_pages if has_kv else None, "krot_pages", proj.dtype),
@@ -593,31 +687,35 @@ def latent_prepare(proj, q_off: int, kv_off: int, qa, positions, seq_of_token, s
 
 
 def head_gemm(a, lda: int, a_head_stride: int, b, b_head_stride: int, b_k_stride: int, b_n_stride: int, c, ldc: int, c_head_stride: int,
-              rows: int, heads: int, n: int, k: int, gate=None, ldg: int = 0, gate_off: int = 0, a_off: int = 0) -> None:
+              rows: int, heads: int, n: int, k: int, gate=None, ldg: int = 0, gate_off: int = 0, a_off: int = 0,
+              gate_per_output: bool = False) -> None:
     """Per head h: ``c[t, h, :n] = a[t, a_off + h * a_head_stride : ... + k] @ B_h`` with
     ``B_h[k, n] = b[h * b_head_stride + k * b_k_stride + n * b_n_stride]``, times ``sigmoid(gate[t * ldg + gate_off + h])``
-    when a gate is given. Float32 accumulation in a fixed order."""
+    when a gate is given (``gate_per_output``: one gate per output, ``gate[t * ldg + gate_off + h * n + j]`` for column j).
+    Float32 accumulation in a fixed order."""
     if a.dtype != b.dtype or c.dtype != a.dtype or (gate is not None and gate.dtype != a.dtype):
         raise KernelError("head_gemm: one element type for all operands")
     item = a.element_size()
     gate_ptr = None if gate is None else _dev(gate, "gate") + gate_off * item
     _check(_fn("stride_head_gemm")(_dev(a, "a") + a_off * item, lda, a_head_stride, _dev(b, "b"), b_head_stride, b_k_stride, b_n_stride,
-                                   _dev(c, "c"), ldc, c_head_stride, gate_ptr, ldg, rows, heads, n, k, _code(a.dtype), _stream()),
+                                   _dev(c, "c"), ldc, c_head_stride, gate_ptr, ldg, n if gate_per_output else 1, 1 if gate_per_output else 0,
+                                   rows, heads, n, k, _code(a.dtype), _stream()),
            "head_gemm")
 
 
 def latent_attention(qa, out, latent_pages, krot_pages, block_table, seq_of_token, positions, heads: int, rank: int, rot: int,
-                     page_size: int, scale: float) -> None:
+                     page_size: int, scale: float, sinks=None) -> None:
     """Causal attention of every token over its request's latent pages: ``qa`` [tokens, heads * (rank + rot)] holds the
-    folded and the rotated query parts, ``out`` [tokens, heads * rank] receives the weighted sums of the latents."""
+    folded and the rotated query parts, ``out`` [tokens, heads * rank] receives the weighted sums of the latents.
+    ``sinks`` (float32 [heads]): exp(sink_h) joins head h's denominator."""
     tokens = out.shape[0]
     if out.shape[1] != heads * rank or qa.shape != (tokens, heads * (rank + rot)):
         raise KernelError("latent_attention: shapes do not agree")
     _check(_fn("stride_latent_attention")(
         _dev(qa, "qa"), _dev(out, "out", qa.dtype), _dev(latent_pages, "latent_pages", qa.dtype), _dev(krot_pages, "krot_pages", qa.dtype),
         _dev(block_table, "block_table", torch.int32), block_table.shape[1], _dev(seq_of_token, "seq_of_token", torch.int32),
-        _dev(positions, "positions", torch.int32), tokens, heads, rank, rot, page_size, float(scale), _code(qa.dtype), _stream()),
-        "latent_attention")
+        _dev(positions, "positions", torch.int32), tokens, heads, rank, rot, page_size, float(scale), _opt(sinks, "sinks", torch.float32),
+        _code(qa.dtype), _stream()), "latent_attention")
 
 
 def latent_tc_supported(dtype, heads: int, rank: int, rot: int) -> bool:
@@ -630,7 +728,7 @@ LATENT_TC = _os.environ.get("STRIDE_B200_LATENT_TC", "1") != "0"
 
 def latent_attention_tc(qa, out, partial, latent_pages, krot_pages, block_table, q_start, q_len, ctx_len, seq_of_token, first_seq: int,
                         num_seqs: int, first_token: int, tokens: int, max_q_len: int, heads: int, rank: int, rot: int, page_size: int,
-                        scale: float, splits: int = 1, keys_per_split: int = 0) -> None:
+                        scale: float, splits: int = 1, keys_per_split: int = 0, sinks=None) -> None:
     """Latent attention on the tensor cores for the requests ``first_seq .. first_seq + num_seqs`` of the step, which own
     ``tokens`` rows from ``first_token`` on (``qa`` and ``out`` are the whole step's). ``max_q_len`` 1 runs the single-token
     form, whose keys may be cut into ``splits`` of ``keys_per_split`` with ``partial`` (float32,
@@ -640,8 +738,8 @@ def latent_attention_tc(qa, out, partial, latent_pages, krot_pages, block_table,
         _dev(latent_pages, "latent_pages", torch.bfloat16), _dev(krot_pages, "krot_pages", torch.bfloat16),
         _dev(block_table, "block_table", torch.int32), block_table.shape[1], _dev(q_start, "q_start", torch.int32),
         _dev(q_len, "q_len", torch.int32), _dev(ctx_len, "ctx_len", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
-        first_seq, num_seqs, first_token, tokens, max_q_len, heads, rank, rot, page_size, float(scale), splits, keys_per_split, _stream()),
-        "latent_attention_tc")
+        first_seq, num_seqs, first_token, tokens, max_q_len, heads, rank, rot, page_size, float(scale), splits, keys_per_split,
+        _opt(sinks, "sinks", torch.float32), _stream()), "latent_attention_tc")
 
 
 # ---------------------------------------------------------------- recurrent block
@@ -719,6 +817,18 @@ def moe_select_sigmoid(logits, correction, seq_of_token, ids, weights, experts: 
                                             int(keep), float(route_scale), _stream()), "moe_select_sigmoid")
 
 
+def moe_select_groups(logits, correction, seq_of_token, ids, weights, experts: int, groups: int, keep: int, route_scale: float,
+                      softmax: bool = False, group_max: bool = False, keep_scores: bool = False) -> None:
+    """``moe_select_sigmoid`` with its rule opened up: ``softmax`` takes the softmax of the logits over all experts as
+    scores (sigmoid otherwise), ``group_max`` counts a group as its largest choice score (the sum of its two largest
+    otherwise), ``keep_scores`` leaves the weights at ``score * route_scale`` (divided by the chosen scores' sum otherwise)."""
+    rule = (1 if softmax else 0) | (2 if group_max else 0) | (4 if keep_scores else 0)
+    _check(_fn("stride_moe_select_groups")(_dev(logits, "logits", torch.float32), logits.shape[1], _opt(correction, "correction", torch.float32),
+                                           _opt(seq_of_token, "seq_of_token", torch.int32), _dev(ids, "ids", torch.int32),
+                                           _dev(weights, "weights", torch.float32), logits.shape[0], int(experts), ids.shape[1], int(groups),
+                                           int(keep), float(route_scale), rule, _stream()), "moe_select_groups")
+
+
 def moe_plan(ids, experts: int, offsets, perm_token, row_of, rank_tmp) -> None:
     tokens, top = ids.shape
     _check(_fn("stride_moe_plan")(_dev(ids, "ids", torch.int32), tokens, top, experts, _dev(offsets, "offsets", torch.int32),
@@ -729,7 +839,8 @@ def moe_plan(ids, experts: int, offsets, perm_token, row_of, rank_tmp) -> None:
 def grouped_gemm(a, row_map, w, offsets, c, max_rows: int, act: int = 0, limit: float = 0.0, alpha: float = 1.0) -> None:
     """For every expert e and row p in ``offsets[e] .. offsets[e+1]``: ``c[p] = act(a[row_map[p]] @ w[e].T)`` (``row_map`` None:
     row p itself). ``w`` [experts, n, k]; ``act`` 1 squares the positive part; ``act`` 2 takes rows 2i and 2i + 1 of ``w[e]`` as
-    gate and up of unit i and leaves ``g' sigmoid(alpha g') (u' + 1)`` (clamped at ``limit``) in ``c`` [rows, n / 2]."""
+    gate and up of unit i and leaves ``g' sigmoid(alpha g') (u' + 1)`` (clamped at ``limit``) in ``c`` [rows, n / 2]; ``act`` 3
+    takes the same pairs and leaves ``g sigmoid(g) u``."""
     experts, n, k = w.shape
     if a.dtype == torch.float32:
         kind = 0

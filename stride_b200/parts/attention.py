@@ -25,6 +25,13 @@ Spec params, all optional:
   al., "Train Short, Test Long: Attention with Linear Biases Enables Input Length Extrapolation", with c = 8).
 * ``output_bias``: a bias ``o.b`` on the output projection. The mixer hands it out as ``output_bias`` and the layer's
   arrangement adds it (the ``output_norm`` arrangement inside its norm's kernel).
+* ``conv`` n: a causal convolution of n taps over time on every channel of the q, k and v projections, directly after the
+  projection (tensors ``q.conv``, ``k.conv``, ``v.conv`` [channels, n], no bias): ``y_t = sum_j w[:, j] u_(t - n + 1 + j)``, zeros
+  before a request's start. The last n - 1 projected rows of a request are its state (one float32 row in a state slot).
+* ``qk_norm`` ``weighted``: every query and key head goes through an RMS norm with a weight of the head's size shared by the
+  heads (tensors ``q.norm``, ``k.norm``; ``norm_eps`` inside the root), after the convolution. One kernel does the
+  convolution, the norms and the write into the pages; a second one moves the tails on.
+* ``sinks`` ``zero``: no tensor; every head's denominator gains exp(0) = 1.
 * ``borrowed_kv``: the mixer has no key and value projections and reads the pages of the cache slot it is given, which
   another layer's mixer of the same shape writes.
 
@@ -39,7 +46,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .base import CacheRequest, Mixer, Projection, TensorDecl, build_part, register_part
+from .base import CacheRequest, Mixer, Projection, StateRequest, TensorDecl, build_part, register_part
 
 
 class PagedAttention(Mixer):
@@ -62,7 +69,9 @@ class PagedAttention(Mixer):
         p = dict(s.params)
         self.values_are_keys = p.get("values") == "keys"
         self.softcap = float(p.get("softcap", 0.0))
-        self.has_sinks, self.gated = bool(p.get("sinks", False)), bool(p.get("output_gate", False))
+        self.zero_sinks = p.get("sinks") == "zero"
+        self.has_sinks, self.gated = bool(p.get("sinks", False)) and not self.zero_sinks, bool(p.get("output_gate", False))
+        self.taps, self.weighted_qk = int(p.get("conv", 0)), p.get("qk_norm") == "weighted"
         self.short_names = p.get("names") == "short"
         self.vd = int(p.get("value_dim", self.hd))
         self.unit_qk, self.unit_v = p.get("qk_norm") == "unit", p.get("v_norm") == "unit"
@@ -77,7 +86,12 @@ class PagedAttention(Mixer):
         # what the plain path (projection, then the position part's rotation and cache write) cannot do goes through
         # the head-norm kernel, which adds the bias, norms and writes the pages itself when there is no rotation
         self.plain_position = s.position is None or s.position.kind == "none"
-        self.own_prepare = self.unit_qk or self.unit_v or self.vd != self.hd or self.borrows
+        self.conv_path = self.taps > 0 or self.weighted_qk
+        if self.conv_path and (self.unit_qk or self.unit_v or self.borrows or s.bias or self.head_gate or not self.plain_position
+                               or not self.short_names or self.taps > 16):
+            raise ValueError("a convolution or weighted head norms go with no rotation, no biases, no unit norms, no borrowed pages, "
+                             "no per-head gate, short tensor names and at most 16 taps")
+        self.own_prepare = self.unit_qk or self.unit_v or self.vd != self.hd or self.borrows or self.conv_path
         if self.own_prepare and not self.plain_position and (self.vd != self.hd or self.borrows):
             raise ValueError("a rotation with borrowed pages or a value width of its own is not supported")
         self.fused_gate = self.head_gate and self.own_prepare and self.plain_position
@@ -91,7 +105,9 @@ class PagedAttention(Mixer):
         self.qkv_dim = self.q_dim + self.kv_cols + self.gate_cols
         permutation = getattr(self.position, "head_permutation", lambda: None)()
         self.perm = None if permutation is None else torch.tensor(permutation, dtype=torch.long)
-        self.w_qkv = self.w_o = self.bias = self.w_gate = self.sinks = None
+        self.w_qkv = self.w_o = self.bias = self.w_gate = self.sinks = self.conv_w = self.wq_norm = self.wk_norm = None
+        if self.zero_sinks:
+            self.sinks = torch.zeros(self.nq, dtype=torch.float32, device=runtime.device)
         self._fast = ops.fast_attention_supported(runtime.dtype, self.nq, self.nkv, self.hd) and self.vd == self.hd
         self.accepts_folded = not self.gated          # the gate reads the normed input as a tensor
 
@@ -125,6 +141,11 @@ class PagedAttention(Mixer):
             d[w["g"]] = TensorDecl((self.nq if self.head_gate else self.q_dim, self.hidden))
         if self.has_sinks:
             d[w["sink"]] = TensorDecl((self.nq,), "vector")
+        p = self.spec.prefix
+        if self.taps:
+            d.update({f"{p}{n}.conv": TensorDecl((rows, self.taps), "vector") for n, rows in (("q", self.q_dim), ("k", self.kv_dim), ("v", self.v_dim))})
+        if self.weighted_qk:
+            d.update({f"{p}{n}.norm": TensorDecl((self.hd,), "vector") for n in "qk"})
         d.update(self.position.declare())          # a position encoding may have tensors of its own
         return d
 
@@ -176,6 +197,11 @@ class PagedAttention(Mixer):
             self.sinks = weights[w["sink"]]
         if self.has_output_bias:
             self.output_bias = weights[b["o"]]
+        p = self.spec.prefix
+        if self.taps:
+            self.conv_w = torch.cat([weights[f"{p}{n}.conv"] for n in "qkv"], dim=0).contiguous()
+        if self.weighted_qk:
+            self.wq_norm, self.wk_norm = weights[p + "q.norm"], weights[p + "k.norm"]
         self.position.bind(weights)
 
     def _named_own(self):
@@ -192,6 +218,12 @@ class PagedAttention(Mixer):
             out[w["sink"]] = self.sinks
         if self.has_output_bias:
             out[b["o"]] = self.output_bias
+        p = self.spec.prefix
+        if self.taps:
+            q, k = self.q_dim, self.q_dim + self.kv_dim
+            out.update({p + "q.conv": self.conv_w[:q], p + "k.conv": self.conv_w[q:k], p + "v.conv": self.conv_w[k:]})
+        if self.weighted_qk:
+            out.update({p + "q.norm": self.wq_norm, p + "k.norm": self.wk_norm})
         out.update(self.position.named_tensors())
         return out
 
@@ -224,6 +256,12 @@ class PagedAttention(Mixer):
             return CacheRequest(window=self.spec.window, tensors=(("k", self.nkv, self.hd), ("v", self.nkv, self.vd)))
         return CacheRequest(self.nkv, self.hd, self.spec.window)
 
+    def state_request(self):
+        """The convolution's tail: the last taps - 1 projected rows of a request, float32."""
+        if self.taps > 1:
+            return StateRequest(((self.taps - 1) * (self.q_dim + self.kv_dim + self.v_dim),), torch.float32)
+        return None
+
     # ----------------------------------------------------------------- forward
     lazy_output = True
     accepts_folded = True       # an instance with an output gate says False
@@ -232,7 +270,13 @@ class PagedAttention(Mixer):
         tokens = x.shape[0]
         qkv = self.rt.buffer("qkv", tokens, self.qkv_dim)
         folded = x if isinstance(x, ops.FoldedNorm) else None
-        if self.own_prepare:
+        if self.conv_path:
+            if folded:
+                x = folded.tensor()
+            raw = self.rt.buffer("qkv_raw", tokens, self.qkv_dim)
+            ops.linear(x, self.w_qkv, raw)
+            self._convolve_and_store(raw, qkv, ctx, cache, tokens)
+        elif self.own_prepare:
             if folded:
                 x = folded.tensor()
             ops.linear(x, self.w_qkv, qkv)
@@ -261,6 +305,16 @@ class PagedAttention(Mixer):
         ops.linear(attn, self.w_o, out)
         return out
 
+
+    def _convolve_and_store(self, raw, qkv, ctx, cache, tokens):
+        """Convolution over time, weighted head norms and the pages in one kernel; then the tails of the step's requests move on."""
+        slots = ctx.slot_mapping[cache.group][:tokens] if cache.writes else None
+        state = cache.state if self.taps > 1 else None
+        ops.conv_head_norm(raw, qkv, self.conv_w, state, 0, ctx.seq_of_token[:tokens], ctx.q_start, ctx.state_slot, self.wq_norm, self.wk_norm,
+                           self.norm_eps, slots, cache.k_pages if cache.writes else None, cache.v_pages if cache.writes else None, self.nq,
+                           self.nkv, self.hd, self.vd, cache.page_size)
+        if state is not None:
+            ops.conv_tail(raw, state, 0, ctx.q_start, ctx.q_len, ctx.state_slot, ctx.q_len.shape[0], self.qkv_dim, self.taps)
 
     def _norm_and_store(self, qkv, ctx, cache, tokens):
         """Bias, head norms and the pages: in one kernel when there is no rotation, else the norms here and rotation and

@@ -17,6 +17,8 @@ PositionEncoding  used by a mixer: ``encode_and_store`` rotates queries and keys
               in place and writes keys and values into the pages.
 StreamInput   ``forward(stream, ctx, scale)``: adds ``scale`` times something made from the step's token ids and the
               stream itself to the stream (a per-layer token input).
+PassInput     ``forward(stream, first, number, ctx)``: reworks the stream before pass ``number`` over a repeated block of
+              layers; ``first`` is the embedding's output in the compute dtype.
 Layer         ``forward(stream, ctx, cache)``: the arrangement of the above.
 Embedding     ``forward(ctx, out)``: fills the float32 residual rows [tokens, hidden]
               from ``ctx.token_ids``; ``table()`` is what a tied head may share.
@@ -36,7 +38,7 @@ import torch
 
 from ..weights import TensorDecl
 
-CATEGORIES = ("norm", "mixer", "feed_forward", "position", "layer", "embedding", "head", "stream_input")
+CATEGORIES = ("norm", "mixer", "feed_forward", "position", "layer", "embedding", "head", "stream_input", "pass_input")
 _PARTS: dict[str, dict[str, type]] = {c: {} for c in CATEGORIES}
 
 
@@ -182,6 +184,12 @@ class StreamInput(Part):
         raise NotImplementedError
 
 
+class PassInput(Part):
+    def forward(self, stream, first, number: int, ctx) -> None:
+        """``stream``: the step's ``ResidualStream``; ``first``: the embedding's output [tokens, hidden] in the compute dtype."""
+        raise NotImplementedError
+
+
 class Layer(Part):
     mixer: Mixer
 
@@ -210,4 +218,4 @@ class Head(Part):
 
 
 __all__ = ["CATEGORIES", "Embedding", "Head", "register_part", "build_part", "registered_parts", "CacheRequest", "StateRequest", "Part", "Norm",
-           "PositionEncoding", "Mixer", "FeedForward", "Layer", "StreamInput", "TensorDecl", "Projection"]
+           "PositionEncoding", "Mixer", "FeedForward", "Layer", "StreamInput", "PassInput", "TensorDecl", "Projection"]

@@ -6,7 +6,10 @@ token-dependent input to the stream after the feed-forward.
 
 ``output_norm``: the sublayers read the stream itself and the norm sits on what they give back,
 ``x += m * norm(mixer(x)); x += m * norm(ffn(x))``. A sublayer's last bias (``output_bias``) is added inside the
-norm's kernel."""
+norm's kernel.
+
+``sandwich``: a norm on either side of a sublayer, ``x += m * out_norm(mixer(norm(x))); x += m * out_norm(ffn(norm(x)))``
+(the spec's ``mixer_out_norm`` and ``ffn_out_norm``; a learned scale on the sum is a param of those norms)."""
 
 from __future__ import annotations
 
@@ -74,5 +77,29 @@ class OutputNormLayer(PreNormLayer):
             part.forward(stream, ctx, mult)
 
 
+class SandwichLayer(PreNormLayer):
+    """Norm, sublayer, norm, sum: the pre-norm kernel in front (the stream is settled, so it only norms), the output norm's
+    kernel behind (norm, multiplier and residual sum in one)."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        if spec.mixer_out_norm is None or (self.feed_forward is not None and spec.ffn_out_norm is None):
+            raise ValueError("the sandwich arrangement needs a norm on every sublayer's output")
+        self.mixer_out_norm = build_part("norm", spec.mixer_out_norm, runtime)
+        self.ffn_out_norm = build_part("norm", spec.ffn_out_norm, runtime) if self.feed_forward is not None else None
+
+    def parts(self):
+        return super().parts() + (self.mixer_out_norm,) + ((self.ffn_out_norm,) if self.ffn_out_norm is not None else ())
+
+    def forward(self, stream, ctx, cache):
+        mixer, ffn, mult = self.mixer, self.feed_forward, self.mult
+        stream.add_normed(mixer.forward(stream.normed(self.mixer_norm), ctx, cache), self.mixer_out_norm, mult, keep_copy=False)
+        if ffn is not None:
+            stream.add_normed(ffn.forward(stream.normed(self.ffn_norm), ctx), self.ffn_out_norm, mult, keep_copy=False)
+        for part in self.after:
+            part.forward(stream, ctx, mult)
+
+
 register_part("layer", "pre_norm", PreNormLayer)
+register_part("layer", "sandwich", SandwichLayer)
 register_part("layer", "output_norm", OutputNormLayer)

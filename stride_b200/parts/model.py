@@ -4,7 +4,9 @@ part chosen by its spec's kind.
 
 The schedule is data: an entry names a layer and a cache slot, so a layer may
 run twice (with two slots, or sharing one) and a run may read the keys and
-values that another run wrote. The step itself follows
+values that another run wrote. An entry may also start a pass over a block of
+layers that runs several times; the model's ``pass_input`` part then reworks the
+stream before it. The step itself follows
 python/stride_worker/model.py:225-346: embedding gather, the layers, the final
 norm on the wanted rows only, and the head on those rows, giving float32 logits.
 """
@@ -28,16 +30,20 @@ class DecoderModel:
         self.layers = [build_part("layer", ls, runtime) for ls in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, runtime)
         self.head = build_part("head", spec.head_spec(), runtime)
+        self.pass_input = build_part("pass_input", spec.pass_input, runtime) if getattr(spec, "pass_input", None) is not None else None
         self.schedule = tuple(spec.schedule)
         for e in self.schedule:
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"the schedule names layer {e.layer}, but there are {len(self.layers)} layers")
+            if getattr(e, "enters_pass", None) is not None and self.pass_input is None:
+                raise ValueError("a schedule entry starts a pass, but the model has no pass input")
         self.caches = None          # list of LayerCache, one per schedule entry; set by DeviceCache.attach
         self.capture = None         # when a list, every run appends the float32 hidden state (diagnostics)
 
     # ----------------------------------------------------------------- weights
     def _parts(self):
-        return [self.embedding, *self.layers, self.final_norm, self.head]
+        extra = [self.pass_input] if self.pass_input is not None else []
+        return [self.embedding, *extra, *self.layers, self.final_norm, self.head]
 
     def declare(self) -> dict:
         d = {}
@@ -104,7 +110,13 @@ class DecoderModel:
         self.embedding.forward(ctx, stream.residual)
         for state in self._states():        # a request that starts in this step finds its state slots at zero
             ops.zero_fresh_state(state, ctx.state_slot, ctx.q_start, ctx.q_len, ctx.positions)
+        first = None
+        if self.pass_input is not None:         # the embedding's output in the compute dtype, for every pass to come
+            first = self.rt.buffer("embedding_out", tokens, self.hidden)
+            ops.norm_add(stream.residual, None, None, None, first, 0.0, 0.0)
         for entry, cache in zip(self.schedule, self.caches):
+            if getattr(entry, "enters_pass", None) is not None:
+                self.pass_input.forward(stream, first, entry.enters_pass, ctx)
             self.layers[entry.layer].forward(stream, ctx, cache)
             if self.capture is not None:
                 self.capture.append(stream.materialize().clone())
@@ -133,4 +145,5 @@ class DecoderModel:
     def graph_safe(self) -> bool:
         """False when a part needs the host's view of the step and therefore cannot
         be replayed from a captured graph."""
-        return all(getattr(p, "graph_safe", True) for layer in self.layers for p in getattr(layer, "parts", lambda: ())())
+        return all(getattr(p, "graph_safe", True) for layer in self.layers for p in getattr(layer, "parts", lambda: ())()) and \
+            getattr(self.pass_input, "graph_safe", True)

@@ -23,6 +23,11 @@ Another family of the same part, chosen by the spec:
   ``correction`` [experts]); the experts form ``groups`` equal groups of neighbours, a group counts as the sum of its two
   largest choice scores, and only experts of the ``keep`` best groups can be chosen; the weights are the chosen scores
   (without the correction) over their sum, times ``route_scale``.
+* ``activation`` ``silu`` makes every expert the plain gated unit ``W_down (silu(W_gate h) * (W_up h))``, laid out and run
+  the same way.
+* param ``router`` ``softmax_groups``: scores are the softmax of z over all experts; a group counts as its largest
+  score; the ``top`` largest scores inside the ``keep`` best groups win; the weights are those scores times
+  ``route_scale``, not divided by their sum. No ``correction`` tensor.
 * param ``shared_gate``: the shared expert's output is multiplied by ``sigmoid(W_sg h)``, one number per token (tensor
   ``shared.sg`` [1, hidden]); its row rides in the router's product.
 """
@@ -43,22 +48,23 @@ class RoutedExperts(FeedForward):
         self.hidden, self.ff = int(spec.hidden), int(spec.intermediate)
         self.experts, self.top, self.shared_ff = int(p["experts"]), int(p["top"]), int(p.get("shared", 0))
         self.router_bias = bool(p.get("router_bias", False))
-        if spec.activation not in ("relu_squared", "swish_clamped"):
-            raise ValueError(f"activation {spec.activation!r} is not supported by the routed experts (relu_squared and swish_clamped are)")
+        if spec.activation not in ("relu_squared", "swish_clamped", "silu"):
+            raise ValueError(f"activation {spec.activation!r} is not supported by the routed experts (relu_squared, swish_clamped and silu are)")
         if not 1 <= self.top <= min(self.experts, 32) or self.experts > 256:
             raise ValueError(f"top {self.top} of {self.experts} experts is not supported (up to 32 of up to 256 are)")
-        self.gated = spec.activation == "swish_clamped"
+        self.gated = spec.activation in ("swish_clamped", "silu")
+        self.clamped = spec.activation == "swish_clamped"
         self.limit, self.alpha = float(p.get("limit", 0.0)), float(p.get("alpha", 1.0))
         self.shared_limit = float(p.get("shared_limit", self.limit))
         self.router_kind = p.get("router", "softmax_top")
         self.groups, self.keep, self.route_scale = int(p.get("groups", 1)), int(p.get("keep", 1)), float(p.get("route_scale", 1.0))
         self.shared_gate = bool(p.get("shared_gate", False))
-        if self.router_kind not in ("softmax_top", "sigmoid_groups"):
-            raise ValueError(f"router {self.router_kind!r} is not known (softmax_top and sigmoid_groups are)")
-        if self.router_kind == "sigmoid_groups" and (self.groups < 1 or self.experts % self.groups or not 1 <= self.keep <= self.groups
+        if self.router_kind not in ("softmax_top", "sigmoid_groups", "softmax_groups"):
+            raise ValueError(f"router {self.router_kind!r} is not known (softmax_top, sigmoid_groups and softmax_groups are)")
+        if self.router_kind != "softmax_top" and (self.groups < 1 or self.experts % self.groups or not 1 <= self.keep <= self.groups
                                                      or self.top > self.keep * (self.experts // self.groups)):
             raise ValueError(f"{self.experts} experts in {self.groups} groups of which {self.keep} stay cannot give {self.top} choices")
-        if self.gated and not (self.limit > 0 and self.shared_limit > 0):
+        if self.clamped and not (self.limit > 0 and self.shared_limit > 0):
             raise ValueError("the clamped activation needs a positive `limit`")
         if self.shared_gate and not self.shared_ff:
             raise ValueError("a gate on the shared expert needs a shared expert")
@@ -148,6 +154,9 @@ class RoutedExperts(FeedForward):
         if self.router_kind == "sigmoid_groups":
             ops.moe_select_sigmoid(logits, self.correction, ctx.seq_of_token[:tokens], ids, weights, self.experts, self.groups, self.keep,
                                    self.route_scale)
+        elif self.router_kind == "softmax_groups":
+            ops.moe_select_groups(logits, None, ctx.seq_of_token[:tokens], ids, weights, self.experts, self.groups, self.keep,
+                                  self.route_scale, softmax=True, group_max=True, keep_scores=True)
         else:
             ops.moe_select(logits if not self.shared_gate else logits[:, :self.experts].contiguous(), self.bias,
                            ctx.seq_of_token[:tokens], ids, weights)
@@ -158,7 +167,7 @@ class RoutedExperts(FeedForward):
         ops.moe_plan(ids, self.experts, offsets, perm, row_of, rank)
         hidden_rows = self.rt.buffer("moe_hidden", tokens, top * self.ff).view(pairs, self.ff)
         y = self.rt.buffer("moe_y", tokens, top * self.hidden, torch.float32).view(pairs, self.hidden)
-        act = 2 if self.gated else 1
+        act = (2 if self.clamped else 3) if self.gated else 1
         if not self._products_tc(x, perm, offsets, hidden_rows, y, tokens, pairs, act):
             ops.grouped_gemm(x, perm, self.w_up, offsets, hidden_rows, pairs, act=act, limit=self.limit, alpha=self.alpha)
             ops.grouped_gemm(hidden_rows, None, self.w_down, offsets, y, pairs, act=0)
@@ -166,11 +175,15 @@ class RoutedExperts(FeedForward):
         if self.shared_ff:
             mid = self.rt.buffer("moe_shared_mid", tokens, self.shared_ff)
             if self.gated:
+                kind = self.spec.activation
                 if not (self.shared_block == ops.GATED_BLOCK
-                        and ops.linear_gated_tc(x, self.shared_up, mid, None, "swish_clamped", self.shared_limit, self.alpha)):
+                        and ops.linear_gated_tc(x, self.shared_up, mid, None, kind, self.shared_limit, self.alpha)):
                     both = self.rt.buffer("moe_shared_gate_up", tokens, 2 * self.shared_ff)
                     ops.linear(x, self.shared_up, both)
-                    ops.gated_act(both, mid, self.shared_block, "swish_clamped", self.shared_limit, self.alpha)
+                    if self.clamped:
+                        ops.gated_act(both, mid, self.shared_block, kind, self.shared_limit, self.alpha)
+                    else:
+                        ops.silu_mul(both, mid, self.shared_block)
             else:
                 ops.linear(x, self.shared_up, mid)
                 ops.relu_squared(mid)

@@ -91,11 +91,12 @@ class ResidualStream:
             self._copy_valid = True
         return copy
 
-    def add_normed(self, delta, norm, scale: float = 1.0, bias=None) -> None:
+    def add_normed(self, delta, norm, scale: float = 1.0, bias=None, keep_copy: bool = True) -> None:
         """``stream += scale * norm(delta + bias)``: the sum for layers that norm a sublayer's output. One kernel, which
-        also refreshes the copy that ``values`` hands out."""
+        also refreshes the copy that ``values`` hands out (``keep_copy`` False: nobody reads the stream itself next, so
+        no copy is written)."""
         self._settle()
-        copy = None if self.rt.dtype == torch.float32 else self.rt.buffer("stream_copy", self.tokens, self.hidden)
+        copy = None if self.rt.dtype == torch.float32 or not keep_copy else self.rt.buffer("stream_copy", self.tokens, self.hidden)
         norm.add_normed(self.residual, self._run(delta), bias, float(scale), copy)
         self._copy_valid = copy is not None
 
