@@ -512,8 +512,42 @@ def compare_configs_tutizen(size: dict, layers: int):
     return ours, llama
 
 
+# Layer sizes for `--compare netusun`: four layers of which the first two run twice (six runs, beside six layers of the other
+# designs): latent attention with a dense feed-forward and windowed attention with a mixture inside the repeated block, then a
+# matrix LSTM with a mixture and windowed attention with a dense feed-forward. Attention of the Llama decoder's head count,
+# grouping and head size; the mixture and the dense inner width are those of the Tutizen sizes, so a token uses as many
+# feed-forward weights in every layer of the three designs.
+NETUSUN_SIZES = {
+    "w1024": dict(latent=dict(heads=8, dim=128, rot_dim=64, vdim=128, kv_rank=256, q_rank=384), lstm=dict(heads=8, dim=128, vdim=128),
+                  conv=4, window=1024),
+    "w2048": dict(latent=dict(heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=768), lstm=dict(heads=16, dim=128, vdim=128),
+                  conv=4, window=1024),
+}
+
+
+def compare_configs_netusun(name: str, layers: int):
+    """(Netusun config.json, Llama config.json) of one size; ``layers`` counts runs and must be 6 here."""
+    size, own = TUTIZEN_SIZES[name], NETUSUN_SIZES[name]
+    _tutizen, llama = compare_configs_tutizen(size, layers)
+    lat = dict(own["latent"], scale=(own["latent"]["dim"] + own["latent"]["rot_dim"]) ** -0.5,
+               rot={"base": 10000.0, "dims": own["latent"]["rot_dim"], "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}})
+    win = {"heads": size["heads"], "kv_heads": size["kv"], "dim": size["dim"], "vdim": size["dim"], "scale": size["dim"] ** -0.5,
+           "conv": own["conv"], "mask": {"size": own["window"]}, "softcap": 30.0}
+    dense = {"kind": "dense", "ff": size["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": size["expert_ff"]}, "shared": {"ff": size["shared_ff"]},
+           "router": {"experts": size["experts"], "top": size["top"], "scale": 2.5, "groups": {"count": size["groups"], "keep": size["keep"]}}}
+    entries = [{"type": "latent_attention", "mixer": lat, "mlp": dense}, {"type": "attention", "mixer": win, "mlp": moe},
+               {"type": "mlstm", "mixer": dict(own["lstm"], gate_cap=15.0), "mlp": moe}, {"type": "attention", "mixer": win, "mlp": dense}]
+    ours = {"architecture": "Netusun", "width": size["width"], "vocab": size["vocab"], "norm": {"eps": 1e-6}, "layers": entries,
+            "loop": {"start": 0, "stop": 2, "times": 2}}
+    llama["tie_word_embeddings"] = True         # as Netusun shares its head with the embedding
+    return ours, llama
+
+
 def _compared(design: str, size_name: str, layers: int):
     """The two configurations of ``--compare design`` at one size."""
+    if design == "netusun":
+        return compare_configs_netusun(size_name, layers)
     if design == "migelix":
         return compare_configs_migelix(MIGELIX_SIZES[size_name], layers)
     if design == "tutizen":
@@ -577,8 +611,9 @@ def _measure_design(config: dict, batch: int, context: int, prompt_len: int, ste
 
 
 def run_compare(args) -> dict:
-    """``--compare nidilix | migelix | tutizen``: prefill and decode throughput of that design at a few layer sizes beside the
-    Llama decoder at equal size, with the device time per class of kernel. Not the headline workload."""
+    """``--compare nidilix | migelix | tutizen | netusun``: prefill and decode throughput of that design at a few layer sizes
+    beside the Llama decoder at equal size, with the device time per class of kernel; Netusun also beside Tutizen, the design
+    whose layers are closest to its own (the same mixture, a norm on a sublayer's output). Not the headline workload."""
     layers = args.layers or 6
     sizes = [s for s in args.compare_sizes.split(",") if s]
     result = {"mode": "compare", "design": args.compare, "beside": "llama", "layers": layers, "dtype": "bf16", "data": "synthetic", "sizes": {}}
@@ -587,6 +622,9 @@ def run_compare(args) -> dict:
         result["sizes"][name] = {
             args.compare: _measure_design(ours, args.batch, args.context, 2048, args.steps, args.warmup),
             "llama": _measure_design(llama, args.batch, args.context, 2048, args.steps, args.warmup)}
+        if args.compare == "netusun":
+            closest = compare_configs_tutizen(TUTIZEN_SIZES[name], layers)[0]
+            result["sizes"][name]["tutizen"] = _measure_design(closest, args.batch, args.context, 2048, args.steps, args.warmup)
     return result
 
 
@@ -686,7 +724,7 @@ def main(argv=None) -> int:
     p.add_argument("--no-breakdown", action="store_true", help="skip the per-class times of one decode step and the prefill")
     p.add_argument("--profile", choices=["decode", "prefill"], default=None,
                    help="run a few eager steps of one kind for a profiler instead of measuring")
-    p.add_argument("--compare", choices=["nidilix", "migelix", "tutizen"], default=None,
+    p.add_argument("--compare", choices=["nidilix", "migelix", "tutizen", "netusun"], default=None,
                    help="instead of the headline workload: this design's prefill and decode beside the Llama decoder at equal size")
     p.add_argument("--compare-sizes", default="w1024,w2048", help="comma-separated names of the sizes to compare")
     args = p.parse_args(argv)

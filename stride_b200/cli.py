@@ -200,7 +200,7 @@ def cmd_diagnose_prefill(args) -> int:
 
 
 def main(argv=None) -> int:
-    parser = argparse.ArgumentParser(prog="stride-b200", description="LLM inference engine for one B200 (Llama 3 dense decoder; Nidilix)")
+    parser = argparse.ArgumentParser(prog="stride-b200", description="LLM inference engine for one B200 (Llama 3 dense decoder; Nidilix, Migelix, Tutizen, Netusun)")
     sub = parser.add_subparsers(dest="command", required=True)
 
     g = sub.add_parser("generate", help="generate tokens for prompts given as token ids")
