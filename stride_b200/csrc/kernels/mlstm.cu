@@ -8,13 +8,12 @@
 //   o  = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6)
 //
 // m starts at zero (a cleared state row), not at minus infinity. The memory is independent over the DV columns of S; along a
-// column the only coupling is the sum over D of a read. A column belongs to 8 neighbouring lanes, lane l holding rows l,
-// l + 8, ... in registers together with the same rows of n (every column's lanes keep n for themselves: D / 8 more
-// multiply-adds a token, and no exchange between columns). A CTA of 128 threads owns 16 columns of one head of one request and
-// walks the request's tokens of the step in order; the inputs of 16 tokens are staged in shared memory at a time (q already
-// times `q_scale`, the two gate logarithms computed once a token). Every thread follows the chain of m itself: its
-// exponentials do not depend on the memory and run beside the sums. The order of every sum depends on the token only, so a
-// token's output is bitwise the same in a whole prompt, in portions or decoded alone.
+// column the only coupling is the sum over D of a read. A column belongs to 8 or 16 neighbouring lanes, lane l holding rows
+// l, l + lanes, ... in registers together with the same rows of n (every column's lanes keep n for themselves: a few more
+// multiply-adds a token, and no exchange between columns). A CTA of 128 threads owns 16 or 8 columns of one head of one
+// request and walks the request's tokens of the step in order; the inputs of 16 (or 8) tokens are staged in shared memory at a time
+// (q already times `q_scale`, the two gate logarithms computed once a token). The order of every sum depends on the token
+// only, so a token's output is bitwise the same in a whole prompt, in portions or decoded alone.
 //
 // State row of a request: S [H, D, DV], then n [H, D], then m [H].
 #include "common.cuh"
@@ -22,13 +21,10 @@
 namespace stride {
 
 constexpr int kLstmThreads = 128;
-constexpr int kLstmLanes = 8;
-constexpr int kLstmCols = kLstmThreads / kLstmLanes;
-constexpr int kLstmChunk = 16;
 
 struct LstmArgs {
     const void* proj;       // [tokens, ld] in the compute type: q of head h at q_off + h * D, k at k_off + h * D, v at v_off + h * DV
-    int ld, q_off, k_off, v_off, is_bf16;
+    int ld, q_off, k_off, v_off;
     const float* gates;     // [tokens, ld_gates] float32: column h the input gate's projection, column H + h the forget gate's
     int ld_gates;
     const float* bias_i;    // [H]
@@ -43,25 +39,37 @@ struct LstmArgs {
     int H, D, DV;
 };
 
-__device__ __forceinline__ float lstm_load(const void* p, size_t i, int is_bf16) {
-    return is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]) : static_cast<const float*>(p)[i];
-}
-
 __device__ __forceinline__ float log_sigmoid_f(float z) { return z >= 0.f ? -log1pf(expf(-z)) : z - log1pf(expf(z)); }
 
-template <int R>
+// LANES lanes share a column, each with R of its rows: D <= LANES * R. What is carried from token to token is one
+// multiply-add an entry of S and n and two operations on m; everything else of a token (its exponentials, the sums over the
+// lanes, the division) hangs off that chain. So:
+// * the inputs of the next chunk are fetched into registers (all loads at once, no branch between them) before the current
+//   chunk is worked through, and stored into the other shared-memory buffer afterwards;
+// * while they are stored, warp 0 follows m through that chunk (lane t holds token t's two gate logarithms; sixteen steps of
+//   max and add in token order, the operands handed round by shuffles) and its lanes make the three exponentials of a token
+//   each, so the loop over a chunk reads them from shared memory;
+// * that loop always runs its full length (tokens past the request's end keep the memory as it is) and is unrolled, so that
+//   the sums, shuffles and divisions of one token stand beside the multiply-adds of the next ones.
+template <typename T, int LANES, int R, int CHUNK = 16>
 __global__ void __launch_bounds__(kLstmThreads)
 mlstm_scan_kernel(const LstmArgs p) {
-    constexpr int DP = R * kLstmLanes;
-    __shared__ float s_q[kLstmChunk][DP], s_k[kLstmChunk][DP];
-    __shared__ float s_v[kLstmChunk][kLstmCols], s_li[kLstmChunk], s_lf[kLstmChunk];
+    constexpr int DP = R * LANES;
+    constexpr int COLS = kLstmThreads / LANES;
+    constexpr int ROW_ITEMS = CHUNK * DP / kLstmThreads;
+    constexpr int V_ITEMS = (CHUNK * COLS + kLstmThreads - 1) / kLstmThreads;
+    static_assert((CHUNK * DP) % kLstmThreads == 0 && CHUNK <= 32, "chunks are shared out evenly");
+    __shared__ float s_q[2][CHUNK][DP], s_k[2][CHUNK][DP];
+    __shared__ float s_v[2][CHUNK][COLS];
+    __shared__ float s_keep[2][CHUNK], s_take[2][CHUNK], s_floor[2][CHUNK];
     const int seq = blockIdx.z, h = blockIdx.y;
     const int len = p.q_len[seq];
     if (len <= 0) return;
     const int start = p.q_start[seq];
-    const int il = threadIdx.x & (kLstmLanes - 1), jc = threadIdx.x / kLstmLanes;
-    const int j = blockIdx.x * kLstmCols + jc;
+    const int il = threadIdx.x & (LANES - 1), jc = threadIdx.x / LANES;
+    const int j = blockIdx.x * COLS + jc;
     const int H = p.H, D = p.D, DV = p.DV;
+    const T* proj = static_cast<const T*>(p.proj);
     float* base = p.state + static_cast<size_t>(p.state_slot[seq]) * p.state_stride;
     float* S_g = base + static_cast<size_t>(h) * D * DV;
     float* n_g = base + static_cast<size_t>(H) * D * DV + static_cast<size_t>(h) * D;
@@ -69,48 +77,91 @@ mlstm_scan_kernel(const LstmArgs p) {
     float S[R], nn[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int i = il + kLstmLanes * r;
+        const int i = il + LANES * r;
         S[r] = (i < D && j < DV) ? S_g[static_cast<size_t>(i) * DV + j] : 0.f;
         nn[r] = i < D ? n_g[i] : 0.f;
     }
-    float m = *m_g;
-    for (int c0 = 0; c0 < len; c0 += kLstmChunk) {
-        const int nt = min(kLstmChunk, len - c0);
-        __syncthreads();            // the chunk before has been read by everybody
-        for (int idx = threadIdx.x; idx < kLstmChunk * DP; idx += kLstmThreads) {
+    float m = *m_g;             // followed by warp 0 only
+    const float bias_i = p.bias_i[h], bias_f = p.bias_f[h];
+
+    float fq[ROW_ITEMS], fk[ROW_ITEMS], fv[V_ITEMS], zi = 0.f, zf = 0.f;
+    auto fetch = [&](int c0) {      // the chunk from local token c0 on, into registers (zeros past the request's end)
+#pragma unroll
+        for (int n = 0; n < ROW_ITEMS; ++n) {
+            const int idx = n * kLstmThreads + threadIdx.x;
             const int tt = idx / DP, i = idx - tt * DP;
-            float q = 0.f, k = 0.f;
-            if (tt < nt && i < D) {
-                const size_t row = static_cast<size_t>(start + c0 + tt) * p.ld;
-                q = lstm_load(p.proj, row + p.q_off + h * D + i, p.is_bf16) * p.q_scale;
-                k = lstm_load(p.proj, row + p.k_off + h * D + i, p.is_bf16);
+            const bool on = c0 + tt < len && i < D;
+            const size_t row = static_cast<size_t>(start + (on ? c0 + tt : 0)) * p.ld + h * D + (on ? i : 0);
+            const float q = to_f32(proj[row + p.q_off]), k = to_f32(proj[row + p.k_off]);
+            fq[n] = on ? q * p.q_scale : 0.f;
+            fk[n] = on ? k : 0.f;
+        }
+#pragma unroll
+        for (int n = 0; n < V_ITEMS; ++n) {
+            const int idx = n * kLstmThreads + threadIdx.x;
+            const int tt = idx / COLS, c = idx - tt * COLS;
+            const int col = blockIdx.x * COLS + c;
+            const bool on = tt < CHUNK && c0 + tt < len && col < DV;
+            const float v = to_f32(proj[static_cast<size_t>(start + (on ? c0 + tt : 0)) * p.ld + p.v_off + h * DV + (on ? col : 0)]);
+            fv[n] = on ? v : 0.f;
+        }
+        if (threadIdx.x < CHUNK) {
+            const bool on = c0 + static_cast<int>(threadIdx.x) < len;
+            const size_t row = static_cast<size_t>(start + (on ? c0 + threadIdx.x : 0)) * p.ld_gates;
+            zi = p.gates[row + h];
+            zf = p.gates[row + H + h];
+        }
+    };
+    auto stash = [&](int buf, int c0) {
+#pragma unroll
+        for (int n = 0; n < ROW_ITEMS; ++n) {
+            const int idx = n * kLstmThreads + threadIdx.x;
+            const int tt = idx / DP, i = idx - tt * DP;
+            s_q[buf][tt][i] = fq[n];
+            s_k[buf][tt][i] = fk[n];
+        }
+#pragma unroll
+        for (int n = 0; n < V_ITEMS; ++n) {
+            const int idx = n * kLstmThreads + threadIdx.x;
+            if (idx < CHUNK * COLS) s_v[buf][idx / COLS][idx % COLS] = fv[n];
+        }
+        if (threadIdx.x < 32) {     // warp 0: the gates of the chunk's tokens and the chain of m through them
+            const int lane = threadIdx.x;
+            const bool live = lane < CHUNK && c0 + lane < len;
+            // a token past the end leaves m as it is: max(0 + m, -inf)
+            const float li = live ? p.cap * tanhf((zi + bias_i) / p.cap) : -INFINITY;
+            const float lf = live ? log_sigmoid_f(p.cap * tanhf((zf + bias_f) / p.cap)) : 0.f;
+            float m_before = 0.f, m_after = 0.f;
+#pragma unroll
+            for (int tt = 0; tt < CHUNK; ++tt) {
+                const float m_new = fmaxf(__shfl_sync(0xffffffffu, lf, tt) + m, __shfl_sync(0xffffffffu, li, tt));
+                if (lane == tt) { m_before = m; m_after = m_new; }
+                m = m_new;
             }
-            s_q[tt][i] = q;
-            s_k[tt][i] = k;
+            if (lane < CHUNK) {
+                s_keep[buf][lane] = live ? expf(lf + m_before - m_after) : 1.f;
+                s_take[buf][lane] = live ? expf(li - m_after) : 0.f;
+                s_floor[buf][lane] = live ? expf(-m_after) : 1.f;
+            }
         }
-        for (int idx = threadIdx.x; idx < kLstmChunk * kLstmCols; idx += kLstmThreads) {
-            const int tt = idx / kLstmCols, c = idx - tt * kLstmCols;
-            const int col = blockIdx.x * kLstmCols + c;
-            s_v[tt][c] = (tt < nt && col < DV) ? lstm_load(p.proj, static_cast<size_t>(start + c0 + tt) * p.ld + p.v_off + h * DV + col, p.is_bf16)
-                                                : 0.f;
-        }
-        if (threadIdx.x < nt) {
-            const size_t row = static_cast<size_t>(start + c0 + threadIdx.x) * p.ld_gates;
-            const float zi = p.gates[row + h] + p.bias_i[h], zf = p.gates[row + H + h] + p.bias_f[h];
-            s_li[threadIdx.x] = p.cap * tanhf(zi / p.cap);
-            s_lf[threadIdx.x] = log_sigmoid_f(p.cap * tanhf(zf / p.cap));
-        }
-        __syncthreads();
-        for (int tt = 0; tt < nt; ++tt) {
-            const float li = s_li[tt], lf = s_lf[tt];
-            const float m_new = fmaxf(lf + m, li);
-            const float keep = expf(lf + m - m_new), take = expf(li - m_new), floor_ = expf(-m_new);
-            m = m_new;
-            const float vj = s_v[tt][jc] * take;
+    };
+
+    fetch(0);
+    stash(0, 0);
+    __syncthreads();
+    int buf = 0;
+    for (int c0 = 0; c0 < len; c0 += CHUNK, buf ^= 1) {
+        const int nt = min(CHUNK, len - c0);
+        const bool more = c0 + CHUNK < len;
+        if (more) fetch(c0 + CHUNK);
+#pragma unroll 4
+        for (int tt = 0; tt < CHUNK; ++tt) {
+            const float keep = s_keep[buf][tt], take = s_take[buf][tt];
+            const float vj = s_v[buf][tt][jc] * take;
             float acc[4] = {0.f, 0.f, 0.f, 0.f}, den[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-                const float kk = s_k[tt][il + kLstmLanes * r], qq = s_q[tt][il + kLstmLanes * r];
+                const float kk = s_k[buf][tt][il + LANES * r], qq = s_q[buf][tt][il + LANES * r];
                 S[r] = fmaf(keep, S[r], kk * vj);
                 nn[r] = fmaf(keep, nn[r], take * kk);
                 acc[r & 3] = fmaf(S[r], qq, acc[r & 3]);
@@ -118,17 +169,19 @@ mlstm_scan_kernel(const LstmArgs p) {
             }
             float num = (acc[0] + acc[1]) + (acc[2] + acc[3]), dot = (den[0] + den[1]) + (den[2] + den[3]);
 #pragma unroll
-            for (int o = 1; o < kLstmLanes; o <<= 1) {
+            for (int o = 1; o < LANES; o <<= 1) {
                 num += __shfl_xor_sync(0xffffffffu, num, o);
                 dot += __shfl_xor_sync(0xffffffffu, dot, o);
             }
-            if (il == 0 && j < DV)
-                p.o[(static_cast<size_t>(start + c0 + tt) * H + h) * DV + j] = num / (fmaxf(fabsf(dot), floor_) + 1e-6f);
+            if (il == 0 && j < DV && tt < nt)
+                p.o[(static_cast<size_t>(start + c0 + tt) * H + h) * DV + j] = num / (fmaxf(fabsf(dot), s_floor[buf][tt]) + 1e-6f);
         }
+        if (more) stash(buf ^ 1, c0 + CHUNK);      // nobody reads that buffer: its chunk was finished before the last barrier
+        __syncthreads();
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int i = il + kLstmLanes * r;
+        const int i = il + LANES * r;
         if (i < D && j < DV) S_g[static_cast<size_t>(i) * DV + j] = S[r];
         if (blockIdx.x == 0 && jc == 0 && i < D) n_g[i] = nn[r];
     }
@@ -153,18 +206,30 @@ int stride_mlstm_scan(const void* proj, int ld, int q_off, int k_off, int v_off,
     if (D > 256 || H > 65535 || num_seqs > 65535) return STRIDE_UNSUPPORTED;
     if (num_seqs == 0) return 0;
     LstmArgs a;
-    a.proj = proj; a.ld = ld; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off; a.is_bf16 = dtype == STRIDE_DTYPE_BF16;
+    a.proj = proj; a.ld = ld; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off;
     a.gates = gates; a.ld_gates = ld_gates; a.bias_i = bias_i; a.bias_f = bias_f; a.cap = cap; a.q_scale = q_scale;
     a.o = o; a.state = state; a.state_stride = state_stride; a.q_start = q_start; a.q_len = q_len; a.state_slot = state_slot;
     a.H = H; a.D = D; a.DV = DV;
-    const dim3 grid((DV + kLstmCols - 1) / kLstmCols, H, num_seqs), block(kLstmThreads);
-    const int rows = (D + kLstmLanes - 1) / kLstmLanes;
-    // a chain of tokens keeps few CTAs busy for long: launched without an early start behind the kernel before it
-    if (rows <= 2) stride::launch_alone(mlstm_scan_kernel<2>, grid, block, 0, stream, a);
-    else if (rows <= 4) stride::launch_alone(mlstm_scan_kernel<4>, grid, block, 0, stream, a);
-    else if (rows <= 8) stride::launch_alone(mlstm_scan_kernel<8>, grid, block, 0, stream, a);
-    else if (rows <= 16) stride::launch_alone(mlstm_scan_kernel<16>, grid, block, 0, stream, a);
-    else stride::launch_alone(mlstm_scan_kernel<32>, grid, block, 0, stream, a);
+    const dim3 block(kLstmThreads);
+    // a chain of tokens keeps few CTAs busy for long: launched without an early start behind the kernel before it.
+    // Heads of up to 32 rows: 8 lanes a column; larger ones 16 lanes, so that a lane holds at most 16 rows.
+    auto run = [&](auto kernel, int lanes) {
+        const int cols = kLstmThreads / lanes;
+        stride::launch_alone(kernel, dim3((DV + cols - 1) / cols, H, num_seqs), block, 0, stream, a);
+    };
+    if (dtype == STRIDE_DTYPE_BF16) {
+        if (D <= 16) run(mlstm_scan_kernel<__nv_bfloat16, 8, 2>, 8);
+        else if (D <= 32) run(mlstm_scan_kernel<__nv_bfloat16, 8, 4>, 8);
+        else if (D <= 64) run(mlstm_scan_kernel<__nv_bfloat16, 16, 4>, 16);
+        else if (D <= 128) run(mlstm_scan_kernel<__nv_bfloat16, 16, 8>, 16);
+        else run(mlstm_scan_kernel<__nv_bfloat16, 16, 16, 8>, 16);        // chunks of 8 tokens: two buffers of 16 would not fit
+    } else {
+        if (D <= 16) run(mlstm_scan_kernel<float, 8, 2>, 8);
+        else if (D <= 32) run(mlstm_scan_kernel<float, 8, 4>, 8);
+        else if (D <= 64) run(mlstm_scan_kernel<float, 16, 4>, 16);
+        else if (D <= 128) run(mlstm_scan_kernel<float, 16, 8>, 16);
+        else run(mlstm_scan_kernel<float, 16, 16, 8>, 16);
+    }
     return STRIDE_LAUNCH_STATUS();
 }
 

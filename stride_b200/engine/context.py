@@ -41,6 +41,9 @@ class StepContext:
     # may be replayed (the longest context of the step, or of any step for a
     # captured graph).
     context_bound: int = 0
+    # Sequence slots that may hold a request for as long as this context's launches may be replayed: the step's requests
+    # for a step that runs once, every slot of its batch bucket for a captured graph. 0: not given (every slot of the arrays).
+    seq_slots: int = 0
     # Host copy of the step's items for parts that loop in Python:
     # (request, first flat row, number of tokens, position of the first token, state slot)
     host_items: list = field(default_factory=list)

@@ -136,7 +136,7 @@ class ModelRunner:
         return make_context(staging.dev, staging.layout, num_tokens, batch.num_seqs, num_rows, max_q_len=batch.max_q_len,
                             max_ctx=batch.max_ctx, decode_only=batch.decode_only, host_items=items,
                             decode_tail_start=0 if for_graph else tail_start, decode_tail_seq=0 if for_graph else tail_seq,
-                            context_bound=bound)
+                            context_bound=bound, seq_slots=staging.layout["seq_cap"] if for_graph else batch.num_seqs)
 
     def _pack(self, staging, batch):
         l = staging.layout

@@ -46,6 +46,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
+from .runtime import sequence_slots
 from .base import CacheRequest, Mixer, Projection, StateRequest, TensorDecl, build_part, register_part
 
 
@@ -314,7 +315,7 @@ class PagedAttention(Mixer):
                            self.norm_eps, slots, cache.k_pages if cache.writes else None, cache.v_pages if cache.writes else None, self.nq,
                            self.nkv, self.hd, self.vd, cache.page_size)
         if state is not None:
-            ops.conv_tail(raw, state, 0, ctx.q_start, ctx.q_len, ctx.state_slot, ctx.q_len.shape[0], self.qkv_dim, self.taps)
+            ops.conv_tail(raw, state, 0, ctx.q_start, ctx.q_len, ctx.state_slot, sequence_slots(ctx), self.qkv_dim, self.taps)
 
     def _norm_and_store(self, qkv, ctx, cache, tokens):
         """Bias, head norms and the pages: in one kernel when there is no rotation, else the norms here and rotation and

@@ -23,6 +23,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
+from .runtime import sequence_slots
 from .base import Mixer, Projection, StateRequest, TensorDecl, register_part
 
 
@@ -92,7 +93,7 @@ class MatrixLstmMixer(Mixer):
         ops.linear(x, self.w_gates, gates)                  # float32 sums: what enters the recurrence is never rounded to 16 bits
         o = self.rt.buffer("mlstm_o", tokens, self.HV, f32)
         ops.mlstm_scan(proj, 0, self.k_off, self.v_off, gates, self.bias_i, self.bias_f, self.cap, self.D ** -0.5, o, cache.state,
-                       ctx.q_start, ctx.q_len, ctx.state_slot, ctx.q_len.shape[0], self.H, self.D, self.DV)
+                       ctx.q_start, ctx.q_len, ctx.state_slot, sequence_slots(ctx), self.H, self.D, self.DV)
         mixed = self.rt.buffer("mlstm_mixed", tokens, self.HV)
         ops.head_norm_gate(o, self.norm_w, True, proj, "sigmoid_compute", mixed, self.H, self.DV, self.norm_eps, gate_off=self.g_off)
         if lazy_output:

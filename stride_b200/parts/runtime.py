@@ -14,6 +14,13 @@ from ..csrc import ops
 from .base import Projection
 
 
+def sequence_slots(ctx) -> int:
+    """How many leading entries of a step's ``q_start / q_len / state_slot`` a kernel with a CTA (or more) a sequence has to
+    cover: ``ctx.seq_slots`` where the step function gives it (the step's requests, or every slot of a captured graph's batch
+    bucket), else the arrays' whole length."""
+    return int(getattr(ctx, "seq_slots", 0) or 0) or int(ctx.q_len.shape[0])
+
+
 class Runtime:
     def __init__(self, device, dtype: torch.dtype, token_capacity: int, row_capacity: int):
         self.device = torch.device(device)
