@@ -50,7 +50,9 @@ __device__ __forceinline__ float log_sigmoid_f(float z) { return z >= 0.f ? -log
 //   max and add in token order, the operands handed round by shuffles) and its lanes make the three exponentials of a token
 //   each, so the loop over a chunk reads them from shared memory;
 // * that loop always runs its full length (tokens past the request's end keep the memory as it is) and is unrolled, so that
-//   the sums, shuffles and divisions of one token stand beside the multiply-adds of the next ones.
+//   the sums, shuffles and divisions of one token stand beside the multiply-adds of the next ones; a lane's rows come in
+//   groups of four neighbours, one 16-byte read of shared memory a group; the quotient is a product with the hardware's
+//   reciprocal (2 units in the last place; the same instruction for every cutting).
 template <typename T, int LANES, int R, int CHUNK = 16>
 __global__ void __launch_bounds__(kLstmThreads)
 mlstm_scan_kernel(const LstmArgs p) {
@@ -59,7 +61,8 @@ mlstm_scan_kernel(const LstmArgs p) {
     constexpr int ROW_ITEMS = CHUNK * DP / kLstmThreads;
     constexpr int V_ITEMS = (CHUNK * COLS + kLstmThreads - 1) / kLstmThreads;
     static_assert((CHUNK * DP) % kLstmThreads == 0 && CHUNK <= 32, "chunks are shared out evenly");
-    __shared__ float s_q[2][CHUNK][DP], s_k[2][CHUNK][DP];
+    constexpr bool QUADS = R % 4 == 0;      // a lane's rows in groups of four neighbours: one 16-byte read of shared memory a group
+    __shared__ __align__(16) float s_q[2][CHUNK][DP], s_k[2][CHUNK][DP];
     __shared__ float s_v[2][CHUNK][COLS];
     __shared__ float s_keep[2][CHUNK], s_take[2][CHUNK], s_floor[2][CHUNK];
     const int seq = blockIdx.z, h = blockIdx.y;
@@ -74,10 +77,12 @@ mlstm_scan_kernel(const LstmArgs p) {
     float* S_g = base + static_cast<size_t>(h) * D * DV;
     float* n_g = base + static_cast<size_t>(H) * D * DV + static_cast<size_t>(h) * D;
     float* m_g = base + static_cast<size_t>(H) * D * DV + static_cast<size_t>(H) * D + h;
+    // lane il of a column's lanes holds the rows 4 LANES g + 4 il + e (g < R / 4, e < 4), or il + LANES r where R is no multiple of 4
+    auto row_of = [&](int r) { return QUADS ? 4 * LANES * (r >> 2) + 4 * il + (r & 3) : il + LANES * r; };
     float S[R], nn[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int i = il + LANES * r;
+        const int i = row_of(r);
         S[r] = (i < D && j < DV) ? S_g[static_cast<size_t>(i) * DV + j] : 0.f;
         nn[r] = i < D ? n_g[i] : 0.f;
     }
@@ -159,13 +164,30 @@ mlstm_scan_kernel(const LstmArgs p) {
             const float keep = s_keep[buf][tt], take = s_take[buf][tt];
             const float vj = s_v[buf][tt][jc] * take;
             float acc[4] = {0.f, 0.f, 0.f, 0.f}, den[4] = {0.f, 0.f, 0.f, 0.f};
+            if constexpr (QUADS) {
+                const float4* k4 = reinterpret_cast<const float4*>(&s_k[buf][tt][4 * il]);
+                const float4* q4 = reinterpret_cast<const float4*>(&s_q[buf][tt][4 * il]);
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const float kk = s_k[buf][tt][il + LANES * r], qq = s_q[buf][tt][il + LANES * r];
-                S[r] = fmaf(keep, S[r], kk * vj);
-                nn[r] = fmaf(keep, nn[r], take * kk);
-                acc[r & 3] = fmaf(S[r], qq, acc[r & 3]);
-                den[r & 3] = fmaf(nn[r], qq, den[r & 3]);
+                for (int g = 0; g < R / 4; ++g) {
+                    const float4 kv = k4[LANES * g], qv = q4[LANES * g];
+                    const float kk[4] = {kv.x, kv.y, kv.z, kv.w}, qq[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        S[4 * g + e] = fmaf(keep, S[4 * g + e], kk[e] * vj);
+                        nn[4 * g + e] = fmaf(keep, nn[4 * g + e], take * kk[e]);
+                        acc[e] = fmaf(S[4 * g + e], qq[e], acc[e]);
+                        den[e] = fmaf(nn[4 * g + e], qq[e], den[e]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const float kk = s_k[buf][tt][il + LANES * r], qq = s_q[buf][tt][il + LANES * r];
+                    S[r] = fmaf(keep, S[r], kk * vj);
+                    nn[r] = fmaf(keep, nn[r], take * kk);
+                    acc[r & 3] = fmaf(S[r], qq, acc[r & 3]);
+                    den[r & 3] = fmaf(nn[r], qq, den[r & 3]);
+                }
             }
             float num = (acc[0] + acc[1]) + (acc[2] + acc[3]), dot = (den[0] + den[1]) + (den[2] + den[3]);
 #pragma unroll
@@ -174,14 +196,14 @@ mlstm_scan_kernel(const LstmArgs p) {
                 dot += __shfl_xor_sync(0xffffffffu, dot, o);
             }
             if (il == 0 && j < DV && tt < nt)
-                p.o[(static_cast<size_t>(start + c0 + tt) * H + h) * DV + j] = num / (fmaxf(fabsf(dot), s_floor[buf][tt]) + 1e-6f);
+                p.o[(static_cast<size_t>(start + c0 + tt) * H + h) * DV + j] = __fdividef(num, fmaxf(fabsf(dot), s_floor[buf][tt]) + 1e-6f);
         }
         if (more) stash(buf ^ 1, c0 + CHUNK);      // nobody reads that buffer: its chunk was finished before the last barrier
         __syncthreads();
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int i = il + LANES * r;
+        const int i = row_of(r);
         if (i < D && j < DV) S_g[static_cast<size_t>(i) * DV + j] = S[r];
         if (blockIdx.x == 0 && jc == 0 && i < D) n_g[i] = nn[r];
     }

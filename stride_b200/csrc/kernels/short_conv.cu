@@ -3,7 +3,7 @@
 // their pages.
 //
 //   conv_head_norm   raw [tokens, ld]: columns [q heads | k heads | v heads] as projected. For channel c of token t
-//                      y_t[c] = sum_j w[c, j] * u_(t - taps + 1 + j)[c]
+//                      y_t[c] = sum_j w[j, c] * u_(t - taps + 1 + j)[c]          (w [taps, C]: a tap's weights side by side)
 //                    where u is the projected value of the same request: a row of this step, or, before the step's first
 //                    token, a row of the request's tail (the last taps - 1 projected rows, float32, in the request's state
 //                    slot; zeros for a request that starts). Then y / sqrt(mean(y^2) + eps) * weight per query and key
@@ -61,7 +61,7 @@ conv_head_norm_kernel(const T* __restrict__ raw, int ld, T* __restrict__ out, in
                     const int src = local - (taps - 1) + j;
                     const float u = src >= 0 ? to_f32(raw[static_cast<size_t>(start + src) * ld + c])
                                              : tail[static_cast<size_t>(taps - 1 + src) * C + c];
-                    acc = fmaf(conv_w[static_cast<size_t>(c) * taps + j], u, acc);
+                    acc = fmaf(conv_w[static_cast<size_t>(j) * C + c], u, acc);
                 }
                 v[i] = acc;
             } else {
@@ -172,8 +172,11 @@ conv_head_norm_vec_kernel(const T* __restrict__ raw, int ld, T* __restrict__ out
 #pragma unroll
                         for (int e = 0; e < V; e += 4) ConvPack<float>::load(row + e, u + e);
                     }
+                    float w[V];
 #pragma unroll
-                    for (int e = 0; e < V; ++e) v[i][e] = fmaf(conv_w[static_cast<size_t>(c + e) * taps + j], u[e], v[i][e]);
+                    for (int e = 0; e < V; e += 4) ConvPack<float>::load(conv_w + static_cast<size_t>(j) * C + c + e, w + e);
+#pragma unroll
+                    for (int e = 0; e < V; ++e) v[i][e] = fmaf(w[e], u[e], v[i][e]);
                 }
             } else {
                 ConvPack<T>::load(raw + static_cast<size_t>(t) * ld + c, v[i]);
@@ -263,7 +266,7 @@ int stride_conv_head_norm(const void* raw, int ld, void* out, int ld_out, const 
     auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
     const int pack = dtype == STRIDE_DTYPE_F32 ? 4 : 8;
     const bool vec = hd % pack == 0 && vd % pack == 0 && ld % pack == 0 && ld_out % pack == 0 && aligned(raw) && aligned(out) &&
-                     aligned(k_pages) && aligned(v_pages) && aligned(wq) && aligned(wk) && aligned(state) && state_stride % 4 == 0 &&
+                     aligned(k_pages) && aligned(v_pages) && aligned(wq) && aligned(wk) && aligned(state) && aligned(conv_w) && state_stride % 4 == 0 &&
                      tail_off % 4 == 0;
     const bool halves = vec && hd <= 16 * pack && vd <= 16 * pack;       // two heads a warp
     const dim3 grid_h(tokens, ((nq + 2 * nkv + 1) / 2 + kConvWarps - 1) / kConvWarps);

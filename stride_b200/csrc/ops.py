@@ -560,11 +560,11 @@ def mlstm_scan(proj, q_off: int, k_off: int, v_off: int, gates, bias_i, bias_f, 
 def conv_head_norm(raw, out, conv_w, state, tail_off: int, seq_of_token, q_start, state_slot, wq, wk, eps: float, slot_mapping, k_pages,
                    v_pages, nq: int, nkv: int, hd: int, vd: int, page_size: int) -> None:
     """From the fused projection ``raw`` [tokens, >= C] (query heads, key heads, value heads; C channels): the causal
-    convolution ``conv_w`` (float32 [C, taps], or None) over a request's projected rows, which before the step's first token
+    convolution ``conv_w`` (float32 [taps, C]: a tap's weights side by side; or None) over a request's projected rows, which before the step's first token
     come from the tail in ``state`` (float32 [slots, n], rows [taps - 1, C] at ``tail_off``); then the RMS norm of every query
     head with the weight ``wq`` and of every key head with ``wk`` (float32 [hd], or None for no norm); into ``out``, and with
     ``slot_mapping`` keys and values into their pages. The tail is not moved: ``conv_tail`` does that afterwards."""
-    taps = 1 if conv_w is None else conv_w.shape[1]
+    taps = 1 if conv_w is None else conv_w.shape[0]
     if out.dtype != raw.dtype or out.shape[0] != raw.shape[0]:
         raise KernelError("conv_head_norm: raw and out must agree in rows and element type")
     _check(_fn("stride_conv_head_norm")(

@@ -200,7 +200,8 @@ class PagedAttention(Mixer):
             self.output_bias = weights[b["o"]]
         p = self.spec.prefix
         if self.taps:
-            self.conv_w = torch.cat([weights[f"{p}{n}.conv"] for n in "qkv"], dim=0).contiguous()
+            # [taps, channels]: a tap's weights of neighbouring channels side by side, as the kernel reads them
+            self.conv_w = torch.cat([weights[f"{p}{n}.conv"] for n in "qkv"], dim=0).t().contiguous()
         if self.weighted_qk:
             self.wq_norm, self.wk_norm = weights[p + "q.norm"], weights[p + "k.norm"]
         self.position.bind(weights)
@@ -222,7 +223,8 @@ class PagedAttention(Mixer):
         p = self.spec.prefix
         if self.taps:
             q, k = self.q_dim, self.q_dim + self.kv_dim
-            out.update({p + "q.conv": self.conv_w[:q], p + "k.conv": self.conv_w[q:k], p + "v.conv": self.conv_w[k:]})
+            stored = self.conv_w.t()
+            out.update({p + "q.conv": stored[:q], p + "k.conv": stored[q:k], p + "v.conv": stored[k:]})
         if self.weighted_qk:
             out.update({p + "q.norm": self.wq_norm, p + "k.norm": self.wk_norm})
         out.update(self.position.named_tensors())

@@ -189,7 +189,7 @@ def test_convolution_head_norms_cache_write_and_tails(gpu, dtype, tol, nq, nkv, 
     k_pages = torch.full((pages, nkv, page, hd), 7.0, dtype=STORED[dtype], device="cuda")
     v_pages = torch.full((pages, nkv, page, vd), 7.0, dtype=STORED[dtype], device="cuda")
     out = torch.zeros(tokens, C + 8, dtype=STORED[dtype], device="cuda")
-    ops.conv_head_norm(raw.cuda(), out, conv_w.cuda() if taps else None, state if keep else None, 5, seq_of, q_start, dev(slots_of_state + [0]),
+    ops.conv_head_norm(raw.cuda(), out, conv_w.t().contiguous().cuda() if taps else None, state if keep else None, 5, seq_of, q_start, dev(slots_of_state + [0]),
                        wq.cuda() if normed else None, wk.cuda() if normed else None, 1e-5, slot_map.cuda(), k_pages, v_pages, nq, nkv, hd, vd, page)
     if keep:
         ops.conv_tail(raw.cuda(), state, 5, q_start, q_len, dev(slots_of_state + [0]), 4, C, taps)
