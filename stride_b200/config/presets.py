@@ -43,7 +43,24 @@ def _nidilix(width, vocab, pattern, recurrent, attention, mlp, side, mult=0.5, e
     return d
 
 
+def _netusun_tiny() -> dict:
+    """Four layers of which the first two run twice: latent attention, windowed attention behind a convolution, a matrix
+    LSTM, windowed attention; a dense feed-forward and small mixtures."""
+    latent = {"heads": 2, "dim": 32, "rot_dim": 16, "vdim": 32, "kv_rank": 64, "q_rank": 48, "scale": 48 ** -0.5,
+              "rot": {"base": 10000.0, "dims": 16, "scaling": {"factor": 2.0, "original": 128, "fast": 16.0, "slow": 1.0}}}
+    windowed = {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 32 ** -0.5, "conv": 3, "mask": {"size": 64}, "softcap": 20.0}
+    moe = {"kind": "moe", "expert": {"ff": 64}, "shared": {"ff": 32},
+           "router": {"experts": 8, "top": 2, "scale": 1.5, "groups": {"count": 4, "keep": 2}}}
+    layers = [{"type": "latent_attention", "mixer": latent, "mlp": {"kind": "dense", "ff": 192}},
+              {"type": "attention", "mixer": windowed, "mlp": copy.deepcopy(moe)},
+              {"type": "mlstm", "mixer": {"heads": 2, "dim": 32, "vdim": 32, "gate_cap": 10.0}, "mlp": copy.deepcopy(moe)},
+              {"type": "attention", "mixer": copy.deepcopy(windowed), "mlp": None}]
+    return {"architecture": "Netusun", "width": 128, "vocab": 384, "norm": {"eps": 1e-6}, "layers": layers,
+            "loop": {"start": 0, "stop": 2, "times": 2}}
+
+
 PRESETS = {
+    "netusun-tiny": _netusun_tiny(),
     "nidilix-tiny": _nidilix(128, 512, "rarb", {"width": 160, "blocks": 5, "conv": 3},
                              {"heads": 4, "dim": 16, "rot_dim": 16, "vdim": 24, "kv_rank": 48, "rot": {"base": 10000.0, "dims": 16},
                               "scale": 32 ** -0.5},

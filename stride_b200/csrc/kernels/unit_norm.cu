@@ -4,6 +4,8 @@
 //
 //   norm_add        residual[t] += m * w * y / sqrt(mean(y^2) + eps),  y = delta[t] (+ bias), and copy[t] = residual[t]
 //                   in the compute dtype (what the next sublayer's products read). Without a delta it only makes the copy.
+//                   With a second weight it also leaves next[t] = w' residual[t] / sqrt(mean(residual[t]^2) + eps'): the
+//                   norm in front of the next sublayer, from the row while it is at hand.
 //   qkv_unit_norm   for every token of a fused projection [q heads | k heads | v heads | anything else]: the bias is
 //                   added, each query and key head (width hd) and each value head (width vd) is divided by its own root
 //                   mean square (no weight; either norm can be switched off), written back in place, and keys and values
@@ -17,7 +19,8 @@ namespace stride {
 
 template <typename T>
 __global__ void norm_add_kernel(float* __restrict__ residual, const T* __restrict__ delta, const float* __restrict__ bias,
-                                const float* __restrict__ weight, T* __restrict__ copy, int hidden, float eps, float mult) {
+                                const float* __restrict__ weight, T* __restrict__ copy, int hidden, float eps, float mult,
+                                const float* __restrict__ next_weight, float next_eps, T* __restrict__ next_out) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float row_buf[];  // hidden floats, then 32 for the reduction
@@ -39,12 +42,21 @@ __global__ void norm_add_kernel(float* __restrict__ residual, const T* __restric
     }
     const float total = block_sum(sq, scratch);
     const float inv = rsqrtf(total / static_cast<float>(hidden) + eps);
+    float sq2 = 0.f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         const float normed = __fmul_rn(__fmul_rn(row_buf[i], inv), weight[i]);
         const float x = __fadd_rn(res[i], __fmul_rn(mult, normed));
         res[i] = x;
         if (copy) copy[t * hidden + i] = from_f32<T>(x);
+        if (next_out) {
+            row_buf[i] = x;             // this thread's own entry: nobody else reads it before the next loop
+            sq2 = fmaf(x, x, sq2);
+        }
     }
+    if (next_out == nullptr) return;
+    const float inv2 = rsqrtf(block_sum(sq2, scratch) / static_cast<float>(hidden) + next_eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        next_out[t * hidden + i] = from_f32<T>(__fmul_rn(__fmul_rn(row_buf[i], inv2), next_weight[i]));
 }
 
 // Packs of 16 bytes of the compute dtype (8 bfloat16 or 4 float32) for the rows whose width is a whole number of them.
@@ -85,7 +97,8 @@ struct Pack<__nv_bfloat16> {
 // packs), 16-byte accesses. A row's result depends on the width and the block size only.
 template <typename T>
 __global__ void norm_add_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta, const float* __restrict__ bias,
-                                    const float* __restrict__ weight, T* __restrict__ copy, int hidden, float eps, float mult) {
+                                    const float* __restrict__ weight, T* __restrict__ copy, int hidden, float eps, float mult,
+                                    const float* __restrict__ next_weight, float next_eps, T* __restrict__ next_out) {
     pdl_trigger();
     pdl_wait();
     constexpr int V = Pack<T>::V;
@@ -130,12 +143,24 @@ __global__ void norm_add_vec_kernel(float* __restrict__ residual, const T* __res
             for (int j = 0; j < V; ++j) sq1 = fmaf(v[j], v[j], sq1);
         }
         const float inv1 = rsqrtf(block_sum(sq1, scratch) / static_cast<float>(hidden) + eps);
+        float sq2 = 0.f;
         if (on) {
 #pragma unroll
             for (int j = 0; j < V; ++j) x[j] = __fadd_rn(x[j], __fmul_rn(mult, __fmul_rn(__fmul_rn(v[j], inv1), w[j])));
 #pragma unroll
             for (int j = 0; j < V; j += 4) Pack<float>::store(res + p * V + j, x + j);
             if (copy) Pack<T>::store(copy + t * hidden + p * V, x);
+#pragma unroll
+            for (int j = 0; j < V; ++j) sq2 = fmaf(x[j], x[j], sq2);
+        }
+        if (next_out == nullptr) return;
+        const float inv2 = rsqrtf(block_sum(sq2, scratch) / static_cast<float>(hidden) + next_eps);
+        if (on) {
+#pragma unroll
+            for (int j = 0; j < V; j += 4) Pack<float>::load(next_weight + p * V + j, w + j);
+#pragma unroll
+            for (int j = 0; j < V; ++j) x[j] = __fmul_rn(__fmul_rn(x[j], inv2), w[j]);
+            Pack<T>::store(next_out + t * hidden + p * V, x);
         }
         return;
     }
@@ -157,6 +182,7 @@ __global__ void norm_add_vec_kernel(float* __restrict__ residual, const T* __res
     }
     const float total = block_sum(sq, scratch);
     const float inv = rsqrtf(total / static_cast<float>(hidden) + eps);
+    float sq2 = 0.f;
     for (int p = threadIdx.x; p < packs; p += blockDim.x) {
         float v[V], w[V], x[V];
 #pragma unroll
@@ -170,6 +196,25 @@ __global__ void norm_add_vec_kernel(float* __restrict__ residual, const T* __res
 #pragma unroll
         for (int j = 0; j < V; j += 4) Pack<float>::store(res + p * V + j, x + j);
         if (copy) Pack<T>::store(copy + t * hidden + p * V, x);
+        if (next_out) {                 // this thread's own packs: nobody else reads them before the next loop
+#pragma unroll
+            for (int j = 0; j < V; j += 4) Pack<float>::store(row_buf + p * V + j, x + j);
+#pragma unroll
+            for (int j = 0; j < V; ++j) sq2 = fmaf(x[j], x[j], sq2);
+        }
+    }
+    if (next_out == nullptr) return;
+    const float inv2 = rsqrtf(block_sum(sq2, scratch) / static_cast<float>(hidden) + next_eps);
+    for (int p = threadIdx.x; p < packs; p += blockDim.x) {
+        float x[V], w[V];
+#pragma unroll
+        for (int j = 0; j < V; j += 4) {
+            Pack<float>::load(row_buf + p * V + j, x + j);
+            Pack<float>::load(next_weight + p * V + j, w + j);
+        }
+#pragma unroll
+        for (int j = 0; j < V; ++j) x[j] = __fmul_rn(__fmul_rn(x[j], inv2), w[j]);
+        Pack<T>::store(next_out + t * hidden + p * V, x);
     }
 }
 
@@ -312,24 +357,27 @@ using namespace stride;
 extern "C" {
 
 int stride_norm_add(float* residual, const void* delta, const float* bias, const float* weight, void* copy, int tokens, int hidden,
-                    float eps, float mult, int dtype, cudaStream_t stream) {
+                    float eps, float mult, const float* next_weight, float next_eps, void* next_out, int dtype, cudaStream_t stream) {
     if (tokens < 0 || hidden <= 0 || (delta != nullptr && weight == nullptr)) return STRIDE_BAD_ARGUMENT;
+    if (next_out != nullptr && (next_weight == nullptr || delta == nullptr)) return STRIDE_BAD_ARGUMENT;
     if (tokens == 0) return 0;
     const int threads = hidden >= 4096 ? 512 : hidden >= 1024 ? 256 : 128;
     const size_t smem = (static_cast<size_t>(hidden) + 32) * sizeof(float);
     if (smem > 200 * 1024) return STRIDE_UNSUPPORTED;
     auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
-    const bool vec = hidden % 8 == 0 && aligned(residual) && aligned(delta) && aligned(bias) && aligned(weight) && aligned(copy);
+    const bool vec = hidden % 8 == 0 && aligned(residual) && aligned(delta) && aligned(bias) && aligned(weight) && aligned(copy) &&
+                     aligned(next_weight) && aligned(next_out);
     if (dtype == STRIDE_DTYPE_F32) {
         auto kernel = vec ? norm_add_vec_kernel<float> : norm_add_kernel<float>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         stride::launch(kernel, dim3(tokens), dim3(threads), smem, stream, residual, static_cast<const float*>(delta), bias,
-                       weight, static_cast<float*>(copy), hidden, eps, mult);
+                       weight, static_cast<float*>(copy), hidden, eps, mult, next_weight, next_eps, static_cast<float*>(next_out));
     } else if (dtype == STRIDE_DTYPE_BF16) {
         auto kernel = vec ? norm_add_vec_kernel<__nv_bfloat16> : norm_add_kernel<__nv_bfloat16>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         stride::launch(kernel, dim3(tokens), dim3(threads), smem, stream, residual,
-                       static_cast<const __nv_bfloat16*>(delta), bias, weight, static_cast<__nv_bfloat16*>(copy), hidden, eps, mult);
+                       static_cast<const __nv_bfloat16*>(delta), bias, weight, static_cast<__nv_bfloat16*>(copy), hidden, eps, mult,
+                       next_weight, next_eps, static_cast<__nv_bfloat16*>(next_out));
     } else {
         return STRIDE_BAD_ARGUMENT;
     }

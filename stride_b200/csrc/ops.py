@@ -122,7 +122,8 @@ _SIGNATURES = {
     "stride_gated_act": ("pointwise", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p]),
     "stride_head_gate": ("pointwise", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_add_sinusoid": ("pointwise", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
-    "stride_norm_add": ("unit_norm", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p]),
+    "stride_norm_add": ("unit_norm", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p, c_float,
+                                      c_void_p, c_int, c_void_p]),
     "stride_qkv_unit_norm": ("unit_norm", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                            c_float, c_int, c_int, c_int, c_void_p]),
     "stride_moe_select_sigmoid": ("moe", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -393,17 +394,22 @@ def add_sinusoid(x, copy, positions, seq_of_token, freq) -> None:
                                       _code(copy.dtype if copy is not None else torch.float32), _stream()), "add_sinusoid")
 
 
-def norm_add(residual, delta, bias, weight, copy, eps: float, mult: float) -> None:
+def norm_add(residual, delta, bias, weight, copy, eps: float, mult: float, next_weight=None, next_eps: float = 0.0, next_out=None) -> None:
     """``residual += mult * weight * y / sqrt(mean(y^2) + eps)`` with ``y = delta (+ bias)`` per row, in float32; ``copy`` (or
-    None) receives the new rows in the compute dtype. ``delta`` None: only the copy is made."""
+    None) receives the new rows in the compute dtype. ``delta`` None: only the copy is made. With ``next_weight`` and
+    ``next_out`` (``delta``'s type) the kernel also leaves the RMS norm of the new rows with that weight and ``next_eps``: the
+    norm in front of the next sublayer."""
     tokens, hidden = residual.shape
     kind = delta if delta is not None else copy
     if kind is None:
         return
     if delta is not None and copy is not None and delta.dtype != copy.dtype:
         raise KernelError("norm_add: delta and copy must have one element type")
+    if next_out is not None and (delta is None or next_out.dtype != delta.dtype or next_out.shape != residual.shape):
+        raise KernelError("norm_add: the next norm's output must have the delta's element type and the stream's shape")
     _check(_fn("stride_norm_add")(_dev(residual, "residual", torch.float32), _opt(delta, "delta"), _opt(bias, "bias", torch.float32),
                                   _opt(weight, "weight", torch.float32), _opt(copy, "copy"), tokens, hidden, float(eps), float(mult),
+                                  _opt(next_weight, "next_weight", torch.float32), float(next_eps), _opt(next_out, "next_out"),
                                   _code(kind.dtype), _stream()), "norm_add")
 
 

@@ -59,5 +59,13 @@ class RMSNorm(Norm):
     def add_normed(self, residual, delta, bias, mult, copy):
         ops.norm_add(residual, delta, bias, self.weight, copy, self.eps, mult)         # norm, sum, write-back and copy in one kernel
 
+    def add_normed_then(self, residual, delta, bias, mult, following, out) -> bool:
+        """``add_normed`` and, from the row while it is at hand, the norm ``following`` of the new rows into ``out``: one
+        kernel for the norm behind a sublayer and the norm in front of the next one. False: not done (another kind of norm)."""
+        if not isinstance(following, RMSNorm):
+            return False
+        ops.norm_add(residual, delta, bias, self.weight, None, self.eps, mult, following.weight, following.eps, out)
+        return True
+
 
 register_part("norm", "rmsnorm", RMSNorm)

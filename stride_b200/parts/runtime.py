@@ -85,6 +85,7 @@ class ResidualStream:
         self._pending = None
         self._scale = 1.0
         self._copy_valid = False        # the compute-dtype copy of the stream is up to date
+        self._pending_normed = None     # (delta, norm, scale, bias): a normed sum left for the next ``normed`` to run with its own norm
 
     def values(self):
         """The stream itself in the compute dtype, for a sublayer that reads it without a norm in between: the
@@ -101,8 +102,13 @@ class ResidualStream:
     def add_normed(self, delta, norm, scale: float = 1.0, bias=None, keep_copy: bool = True) -> None:
         """``stream += scale * norm(delta + bias)``: the sum for layers that norm a sublayer's output. One kernel, which
         also refreshes the copy that ``values`` hands out (``keep_copy`` False: nobody reads the stream itself next, so
-        no copy is written)."""
+        no copy is written; the sum is then left for the next ``normed``, whose norm the same kernel can apply to the new
+        rows, and runs alone as soon as anything else asks for the stream)."""
         self._settle()
+        if not keep_copy and hasattr(norm, "add_normed_then"):
+            self._pending_normed = (self._run(delta), norm, float(scale), bias)
+            self._copy_valid = False
+            return
         copy = None if self.rt.dtype == torch.float32 or not keep_copy else self.rt.buffer("stream_copy", self.tokens, self.hidden)
         norm.add_normed(self.residual, self._run(delta), bias, float(scale), copy)
         self._copy_valid = copy is not None
@@ -117,6 +123,10 @@ class ResidualStream:
 
     def _settle(self) -> None:
         """Applies what is pending to the residual."""
+        if self._pending_normed is not None:
+            delta, norm, scale, bias = self._pending_normed
+            self._pending_normed = None
+            norm.add_normed(self.residual, delta, bias, scale, None)
         if self._pending is not None:
             p = self._pending
             if self._scale != 1.0:
@@ -141,6 +151,16 @@ class ResidualStream:
         takes an ``ops.FoldedNorm`` too: when the pending delta is a deferred product
         and the norm allows it, product, sum and the norm's statistics become one
         kernel and the norm's scaling is left to the consumer."""
+        if self._pending_normed is not None and rows is None:
+            delta, behind, scale, bias = self._pending_normed
+            out = self.rt.buffer(tag, self.tokens, self.hidden)
+            if behind.add_normed_then(self.residual, delta, bias, scale, norm, out):
+                self._pending_normed = None
+                return out
+        if self._pending_normed is not None:        # not fused after all: the normed sum runs alone (nothing else is pending beside it)
+            delta, behind, scale, bias = self._pending_normed
+            self._pending_normed = None
+            behind.add_normed(self.residual, delta, bias, scale, None)
         if self._scale != 1.0:
             return self._normed_scaled(norm, rows, tag)
         if rows is None and fold_ok and isinstance(self._pending, Projection):

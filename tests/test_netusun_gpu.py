@@ -374,7 +374,20 @@ def test_scaled_output_norm(gpu):
         stream = ResidualStream(rt, 6, width)
         stream.residual.copy_(x)
         stream.add_normed(y.cuda(), norm, 1.0, keep_copy=False)
-        close(stream.materialize(), x.double() + plain.rms_norm(y.double(), w.double(), 1e-3) * s.double(), 3e-6)
+        want = x.double() + plain.rms_norm(y.double(), w.double(), 1e-3) * s.double()
+        close(stream.materialize(), want, 3e-6)
+        # left for the next norm, the sum and that norm are one kernel; asked for rows only, the sum runs alone first
+        front = build_part("norm", NormSpec("rmsnorm", width, 1e-5, "f", (("tensor", "f"),)), rt)
+        front.bind({"f": (w * 0.5 + 0.2).cuda()})
+        stream.add_normed(y.cuda(), norm, 0.5, keep_copy=False)
+        want = want + 0.5 * plain.rms_norm(y.double(), w.double(), 1e-3) * s.double()
+        close(stream.normed(front), plain.rms_norm(want, (w * 0.5 + 0.2).double(), 1e-5), 3e-6)
+        close(stream.materialize(), want, 3e-6)
+        stream.add_normed(y.cuda(), norm, -0.25, keep_copy=False)
+        want = want - 0.25 * plain.rms_norm(y.double(), w.double(), 1e-3) * s.double()
+        close(stream.normed(front, rows=torch.tensor([4, 1], dtype=torch.int32, device="cuda")),
+              plain.rms_norm(want[[4, 1]], (w * 0.5 + 0.2).double(), 1e-5), 3e-6)
+        close(stream.materialize(), want, 3e-6)
 
 
 # ------------------------------------------------------------------- each mechanism in a model of nothing else
